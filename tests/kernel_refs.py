@@ -65,9 +65,20 @@ def embed_rows(table, tokens, out, scale=1.0):
     return out
 
 
-def add_rmsnorm(residual, delta, scale, eps, out, kind="l2_eps"):
+def _norm_factor(x, eps, kind):
+    d = x.shape[-1]
+    if kind == "mean_eps":
+        return 1.0 / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    return math.sqrt(d) / (x.pow(2).sum(-1, keepdim=True).sqrt() + eps)
+
+
+def add_rmsnorm(residual, delta, scale, eps, out, kind="l2_eps", delta_norm=None):
     if delta is not None:
-        residual += delta.to(torch.float32)
+        d32 = delta.to(torch.float32)
+        if delta_norm is not None:
+            dw, deps, dkind = delta_norm
+            d32 = d32 * _norm_factor(d32, deps, dkind) * dw
+        residual += d32
     if out is None:
         return None
     d = residual.shape[-1]
@@ -99,6 +110,28 @@ def glu_clamped(gu, gate_bias, up_bias, limit, alpha, shift, out, hidden):
 def scale_f32(x, scale):
     x *= scale
     return x
+
+
+def softcap_f32(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
+def activation(x, out, kind):
+    z = x.to(torch.float32)
+    if kind == "relu2":
+        y = torch.clamp(z, min=0.0) ** 2
+    elif kind == "gelu_tanh":
+        y = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+    else:
+        y = z * torch.sigmoid(z)
+    out.copy_(y.to(out.dtype))
+    return out
+
+
+def gemm_act(a, w, kind):
+    h = gemm(a, w)
+    return activation(h, h, kind)
 
 
 def _segments(row_slot):
@@ -161,7 +194,7 @@ def norm_mix_store(qkv, nq, nk, nv, q_weight, k_weight, eps, v_other, mix, k_pag
 
 
 def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row_slot, num_heads, page_size, window,
-                     scale, bias_slope, bias_rate, fault, step=None, sink=None):
+                     scale, bias_slope, bias_rate, fault, step=None, sink=None, gate_per_head=False):
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     g = num_heads // kv_heads
     for r in range(q.shape[0]):
@@ -181,8 +214,11 @@ def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row
         if sink is not None:               # one more term in the denominator, without a value
             s = torch.cat([s, sink.to(torch.float32)[:, None]], dim=-1)
         w = torch.softmax(s, dim=-1)[:, :idx.shape[0]]
-        o = torch.einsum("hk,khd->hd", w, v).reshape(-1)
-        if gate is not None:
+        o = torch.einsum("hk,khd->hd", w, v)
+        if gate is not None and gate_per_head:
+            o = o * torch.sigmoid(gate[r, :num_heads].to(torch.float32))[:, None]
+        o = o.reshape(-1)
+        if gate is not None and not gate_per_head:
             o = o * torch.sigmoid(gate[r].to(torch.float32))
         out[r] = o.to(out.dtype)
     return out
@@ -242,12 +278,73 @@ def linear_attention(qkv, gate, decay, norm_weight, eps, state, out, row_slot, r
     return out
 
 
+def forget_gate_recurrence(qv, f_in, lower, f_bias, norm_weight, eps, state, out, row_slot, row_last, num_heads, k_dim,
+                           v_dim, requests=None, segments=None):
+    H = num_heads
+    nq = H * k_dim
+    low = lower.to(torch.float32).view(H, k_dim)
+    for r0, rows, slot in _segments(row_slot):
+        S = state[slot, :H * k_dim * v_dim].reshape(H, k_dim, v_dim).to(torch.float32).clone()
+        for r in range(r0, r0 + rows):
+            row = qv[r].to(torch.float32)
+            q = torch.nn.functional.silu(row[:nq]).view(H, k_dim)
+            v = row[nq:nq + H * v_dim].view(H, v_dim)
+            f = low + (1.0 - low) * torch.sigmoid(f_in[r].to(torch.float32).view(H, k_dim) + f_bias.view(H, k_dim))
+            S = f[:, :, None] * S + (1.0 - f)[:, :, None] * v[:, None, :]
+            o = torch.einsum("hdv,hd->hv", S, q)
+            o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_weight
+            out[r] = o.reshape(-1).to(out.dtype)
+        state[slot, :H * k_dim * v_dim] = S.reshape(-1)
+    return out
+
+
+def head_norm_store(qkv, num_heads, kv_heads, maps, dim, v_dim, bias, q_weight, k_weight, eps, temp_coef, temp_every,
+                    q_out, k_pages, v_pages, block_table, positions, row_slot, page_size, fault):
+    H, G, M = num_heads, kv_heads, maps
+    nq, nk, nv = H * M * dim, G * M * dim, G * v_dim
+    for r in range(qkv.shape[0]):
+        slot = int(row_slot[r])
+        if slot < 0:
+            continue
+        pos = int(positions[r])
+        row = qkv[r, :nq + nk + nv].to(torch.float32)
+        if bias is not None:
+            row = row + bias
+        q, k, v = row[:nq].view(H, M, dim), row[nq:nq + nk].view(G, M, dim), row[nq + nk:].view(G, v_dim)
+        if q_weight is not None:
+            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+        if k_weight is not None:
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if temp_every > 0:
+            q = q * (1.0 + temp_coef * math.log((pos + 1) // temp_every + 1.0))
+        wide = torch.zeros((H, M, M, dim), dtype=torch.float32)
+        for m in range(M):
+            wide[:, m, m] = q[:, m]
+        q_out[r] = wide.reshape(-1).to(q_out.dtype)
+        page = int(block_table[slot, pos // page_size])
+        if page < 0 or page >= k_pages.shape[0]:
+            fault[0] = 7
+            continue
+        k_pages[page, :, pos % page_size, :] = k.reshape(G, M * dim).to(k_pages.dtype)
+        v_pages[page, :, pos % page_size, :] = v.to(v_pages.dtype)
+
+
+def diff_combine(a, lam, eps, out_scale, out, num_heads, v_dim, row_slot=None):
+    x = a.to(torch.float32).view(a.shape[0], num_heads, 2, v_dim)
+    o = x[:, :, 0] - lam * x[:, :, 1]
+    o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+    out.copy_(o.reshape(a.shape[0], -1).to(out.dtype))
+    return out
+
+
 def latent_prepare(proj, dkv_at, num_heads, flat_dim, rot_dim, rank, c_weight, eps, cos, sin, q_out, k_pages, block_table,
                    positions, row_slot, page_size, fault):
-    half = cos.shape[1]
+    half = cos.shape[1] if cos is not None else 0
     qd, row_w = flat_dim + rot_dim, rank + rot_dim
 
     def turn(x, c, s):
+        if half == 0:
+            return x
         a, b = x[..., :half], x[..., half:2 * half]
         return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * half:]], dim=-1)
 
@@ -257,7 +354,7 @@ def latent_prepare(proj, dkv_at, num_heads, flat_dim, rot_dim, rank, c_weight, e
             continue
         pos = int(positions[r])
         row = proj[r].to(torch.float32)
-        c, s = cos[pos], sin[pos]
+        c, s = (cos[pos], sin[pos]) if cos is not None else (None, None)
         q_rot = row[:num_heads * qd].view(num_heads, qd)[:, flat_dim:]
         q_out[r].view(num_heads, row_w)[:, rank:] = turn(q_rot, c, s).to(q_out.dtype)
         low = row[dkv_at:dkv_at + row_w]
@@ -557,6 +654,7 @@ def bitmap_set(bitmap_row, tokens):
 
 _NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set", "glu_clamped", "scale_f32", "causal_conv",
+          "softcap_f32", "activation", "gemm_act", "forget_gate_recurrence", "head_norm_store", "diff_combine",
           "norm_mix_store", "window_attention", "delta_rule", "linear_attention", "latent_prepare", "gemm_heads", "moe_route",
           "moe_gate_up", "moe_down", "moe_experts"]
 

@@ -482,3 +482,127 @@ class MizidraConfig:
         if self.eos_token_id is not None:
             d["eos_token_id"] = self.eos_token_id
         return d
+
+
+@dataclass
+class BiruvikConfig:
+    """Configuration of the Biruvik decoder: a scaled embedding; layers with a norm in front of and behind every
+    sublayer, each norm with one number as its weight; three kinds of mixer; a dense feed-forward without a gate;
+    logits from a matrix of its own, bounded smoothly.
+
+    ``config.json`` is nested: ``vocab``, ``width``, ``norm.eps``, ``embedding.scale``, ``logit_softcap`` (null or
+    absent: none) and ``layers``, a list with, per layer, ``type``, ``mixer`` (the sizes and constants of that kind
+    of mixer) and ``mlp`` (null: none).  The kinds:
+
+    * ``attention`` — ``heads, kv_heads, dim, vdim, scale, diff`` and optionally ``q_temp`` = ``coef, every`` and
+      ``mask.size``: attention whose heads each subtract a second softmax map from the first;
+    * ``latent_attention`` — ``heads, dim, vdim, kv_rank, scale`` and optionally ``mask.size``: attention whose keys
+      and values are expanded from a compressed vector per token, in a sliding window, one sigmoid gate per head;
+    * ``hgrn2`` — ``heads, dim, vdim``: a matrix state per head whose forget gate also decides what is written.
+
+    ``mlp``: ``kind`` ``dense``, ``ff`` and optionally ``act`` (``relu2`` unless given).  The design has no context
+    limit of its own: ``max_context`` (optional) bounds what the engine lays out (block tables)."""
+
+    architecture: ClassVar[str] = "Biruvik"
+    MIXERS: ClassVar[tuple] = ("attention", "latent_attention", "hgrn2")
+    ACTS: ClassVar[tuple] = ("relu2", "gelu_tanh", "silu")
+
+    vocab_size: int
+    hidden_size: int
+    layers: list
+    rms_norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    logit_softcap: Optional[float] = None
+    max_context: int = 1 << 16
+    eos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        errs = []
+        for name in ("vocab_size", "hidden_size"):
+            if not _positive_int(getattr(self, name)):
+                errs.append(f"{name} must be a positive integer, got {getattr(self, name)!r}")
+        if not isinstance(self.layers, list) or not self.layers:
+            errs.append("layers must be a non-empty list")
+            raise ConfigError("; ".join(errs))
+        if not (self.rms_norm_eps >= 0):
+            errs.append(f"norm.eps must be >= 0, got {self.rms_norm_eps}")
+        if not _positive_int(self.max_context):
+            errs.append(f"max_context must be positive, got {self.max_context}")
+        if self.logit_softcap is not None and not (self.logit_softcap > 0):
+            errs.append(f"logit_softcap must be positive or null, got {self.logit_softcap}")
+        num = (int, float)
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, dict) else None
+            if kind not in self.MIXERS:
+                errs.append(f"layers[{i}].type must be one of {self.MIXERS}, got {kind!r}")
+                continue
+            m = layer.get("mixer")
+            if not isinstance(m, dict):
+                errs.append(f"layers[{i}].mixer is missing")
+                continue
+            need = {"attention": ("heads", "kv_heads", "dim", "vdim"),
+                    "latent_attention": ("heads", "dim", "vdim", "kv_rank"),
+                    "hgrn2": ("heads", "dim", "vdim")}[kind]
+            bad = [k for k in need if not _positive_int(m.get(k))]
+            if bad:
+                errs.append(f"layers[{i}].mixer: {', '.join(bad)} must be positive integers")
+                continue
+            if kind != "hgrn2":
+                if not isinstance(m.get("scale"), num) or isinstance(m.get("scale"), bool):
+                    errs.append(f"layers[{i}].mixer.scale is missing")
+                mask = m.get("mask")
+                if mask is not None and not (isinstance(mask, dict) and _positive_int(mask.get("size"))):
+                    errs.append(f"layers[{i}].mixer.mask.size must be a positive integer")
+            if kind == "attention":
+                if m["heads"] % m["kv_heads"]:
+                    errs.append(f"layers[{i}].mixer: {m['heads']} heads are not a multiple of {m['kv_heads']} kv heads")
+                if not isinstance(m.get("diff"), num) or isinstance(m.get("diff"), bool):
+                    errs.append(f"layers[{i}].mixer.diff is missing")
+                t = m.get("q_temp")
+                if t is not None and not (isinstance(t, dict) and isinstance(t.get("coef"), num)
+                                          and _positive_int(t.get("every"))):
+                    errs.append(f"layers[{i}].mixer.q_temp needs coef and a positive integer every")
+            f = layer.get("mlp")
+            if f is None:
+                continue
+            if not isinstance(f, dict) or f.get("kind") != "dense":
+                errs.append(f"layers[{i}].mlp.kind must be 'dense', got {f.get('kind') if isinstance(f, dict) else f!r}")
+            elif not _positive_int(f.get("ff")):
+                errs.append(f"layers[{i}].mlp.ff must be a positive integer")
+            elif f.get("act", "relu2") not in self.ACTS:
+                errs.append(f"layers[{i}].mlp.act must be one of {self.ACTS}, got {f.get('act')!r}")
+        if self.torch_dtype not in ("bfloat16", "float32"):
+            errs.append(f"torch_dtype must be bfloat16 or float32, got {self.torch_dtype!r}")
+        if errs:
+            raise ConfigError("; ".join(errs))
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "BiruvikConfig":
+        missing = [k for k in ("vocab", "width", "layers") if k not in raw]
+        if missing:
+            raise ConfigError(f"config for architecture {cls.architecture!r}: missing keys: " + ", ".join(missing))
+        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=copy.deepcopy(raw["layers"]))
+        if isinstance(raw.get("norm"), dict) and "eps" in raw["norm"]:
+            d["rms_norm_eps"] = float(raw["norm"]["eps"])
+        if isinstance(raw.get("embedding"), dict) and "scale" in raw["embedding"]:
+            d["embedding_scale"] = float(raw["embedding"]["scale"])
+        if raw.get("logit_softcap") is not None:
+            d["logit_softcap"] = float(raw["logit_softcap"])
+        for k in ("max_context", "eos_token_id", "torch_dtype"):
+            if k in raw:
+                d[k] = raw[k]
+        return cls(**d)
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+             "embedding": {"scale": self.embedding_scale}, "logit_softcap": self.logit_softcap,
+             "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layers), "max_context": self.max_context,
+             "torch_dtype": self.torch_dtype}
+        if self.eos_token_id is not None:
+            d["eos_token_id"] = self.eos_token_id
+        return d

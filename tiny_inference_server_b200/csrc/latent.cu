@@ -26,12 +26,12 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int
     const int pos = positions[r];
     const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
     const int half = dims / 2, rest = rot - dims, tid = threadIdx.x, nthr = blockDim.x;
-    if (pos < 0 || pos >= table_rows || page < 0 || page >= num_pages) {
+    if (pos < 0 || (dims > 0 && pos >= table_rows) || page < 0 || page >= num_pages) {
         if (tid == 0) atomicExch(fault, 6);
         return;
     }
-    const float* cs = cos_t + (size_t)pos * half;
-    const float* sn = sin_t + (size_t)pos * half;
+    const float* cs = dims > 0 ? cos_t + (size_t)pos * half : nullptr;     // rot 0: nothing is rotated, the tables may be null
+    const float* sn = dims > 0 ? sin_t + (size_t)pos * half : nullptr;
     pdl_wait();
     const T* row = proj + (size_t)r * ld;
     const int qd = flat + rot, rw = rank + rot;
@@ -69,8 +69,8 @@ TIS_API int tis_latent_prepare(int dtype, const void* proj, int ld, int dkv_at, 
                                const int* block_table, int bt_stride, const int* positions, const int* row_slot,
                                int* fault, int n, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
-    if (H <= 0 || flat < 0 || rot <= 0 || dims <= 0 || dims % 2 || dims > rot || rank <= 0 || page_size <= 0 ||
-        dkv_at < H * (flat + rot)) {
+    if (H <= 0 || flat < 0 || rot < 0 || dims < 0 || dims % 2 || dims > rot || rank <= 0 || page_size <= 0 ||
+        dkv_at < H * (flat + rot) || (dims > 0 && (cos_t == nullptr || sin_t == nullptr))) {
         tis_set_error("latent_prepare: %d heads, %d + %d query elements a head of which %d rotated, rank %d, page size %d", H,
                       flat, rot, dims, rank, page_size);
         return TIS_BAD_SIZE;

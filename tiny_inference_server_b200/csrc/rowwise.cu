@@ -46,7 +46,8 @@ TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, floa
 // ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict__ delta,
-                                   const float* __restrict__ scale, NormFactor factor, T* __restrict__ out, int d) {
+                                   const float* __restrict__ scale, NormFactor factor, T* __restrict__ out, int d,
+                                   const float* __restrict__ dw, NormFactor dfactor) {
     extern __shared__ float row[];
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -54,6 +55,22 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
     const size_t base = (size_t)blockIdx.x * d;
     constexpr int N = Vec16<T>::N;
     const bool vec = (d % N == 0);
+    // dw given: the update passes a norm of its own on its way into the stream, delta * dfactor(its sum of squares) * dw
+    float df = 1.f;
+    if (dw != nullptr && delta != nullptr) {
+        float ds = 0.f;
+        if (vec) {
+            for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+                float dv[N];
+                Vec16<T>::load(delta + base + i, dv);
+#pragma unroll
+                for (int j = 0; j < N; ++j) ds = fmaf(dv[j], dv[j], ds);
+            }
+        } else {
+            for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = to_f32(delta[base + i]); ds = fmaf(v, v, ds); }
+        }
+        df = dfactor.of(block_sum(ds, red));
+    }
     float ss = 0.f;
     if (vec) {
         for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
@@ -66,8 +83,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
             if (delta != nullptr) {
                 float dv[N];
                 Vec16<T>::load(delta + base + i, dv);
+                if (dw != nullptr) {
 #pragma unroll
-                for (int j = 0; j < N; ++j) v[j] += dv[j];
+                    for (int j = 0; j < N; ++j) v[j] = fmaf(dv[j] * df, dw[i + j], v[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) v[j] += dv[j];
+                }
 #pragma unroll
                 for (int j = 0; j < N; j += 4)
                     *reinterpret_cast<float4*>(res + base + i + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -79,7 +101,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
             float v = res[base + i];
             if (delta != nullptr) {
-                v += to_f32(delta[base + i]);
+                v = dw != nullptr ? fmaf(to_f32(delta[base + i]) * df, dw[i], v) : v + to_f32(delta[base + i]);
                 res[base + i] = v;
             }
             row[i] = v;
@@ -106,7 +128,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
 template <typename T, int CH>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, const float* __restrict__ scale,
-                        NormFactor factor, T* __restrict__ out, int n, int d) {
+                        NormFactor factor, T* __restrict__ out, int n, int d, const float* __restrict__ dw,
+                        NormFactor dfactor) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int N = Vec16<T>::N;
@@ -116,6 +139,36 @@ add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, co
     const size_t base = (size_t)r * d;
     float v[CH][N];
     float ss = 0.f;
+    if (dw != nullptr && delta != nullptr) {
+        // the update passes a norm of its own first: it waits in the registers that then take the stream
+        float ds = 0.f;
+#pragma unroll
+        for (int k = 0; k < CH; ++k) {
+            const int i = (lane + 32 * k) * N;
+            if (i < d) {
+                Vec16<T>::load(delta + base + i, v[k]);
+#pragma unroll
+                for (int j = 0; j < N; ++j) ds = fmaf(v[k][j], v[k][j], ds);
+            }
+        }
+        const float df = dfactor.of(warp_sum(ds));
+#pragma unroll
+        for (int k = 0; k < CH; ++k) {
+            const int i = (lane + 32 * k) * N;
+            if (i < d) {
+#pragma unroll
+                for (int j = 0; j < N; j += 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(res + base + i + j);
+                    const float4 w = *reinterpret_cast<const float4*>(dw + i + j);
+                    v[k][j] = fmaf(v[k][j] * df, w.x, x.x); v[k][j + 1] = fmaf(v[k][j + 1] * df, w.y, x.y);
+                    v[k][j + 2] = fmaf(v[k][j + 2] * df, w.z, x.z); v[k][j + 3] = fmaf(v[k][j + 3] * df, w.w, x.w);
+                    *reinterpret_cast<float4*>(res + base + i + j) = make_float4(v[k][j], v[k][j + 1], v[k][j + 2], v[k][j + 3]);
+                }
+#pragma unroll
+                for (int j = 0; j < N; ++j) ss += v[k][j] * v[k][j];
+            }
+        }
+    } else
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
         const int i = (lane + 32 * k) * N;
@@ -159,21 +212,26 @@ add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, co
 
 template <typename T, int CH>
 static void launch_add_rmsnorm_rows(float* residual, const T* delta, const float* scale, NormFactor eps, T* out, int n,
-                                    int d, cudaStream_t stream) {
+                                    int d, const float* dw, NormFactor dfactor, cudaStream_t stream) {
     const int threads = 128;          // four rows a CTA (measured at 2048 x 1536: 9.0 us; eight rows 10.0 us)
     const int rows = threads / 32;
     tis_launch(add_rmsnorm_rows_kernel<T, CH>, dim3((n + rows - 1) / rows), dim3(threads), 0, stream, residual, delta, scale,
-               eps, out, n, d);
+               eps, out, n, d, dw, dfactor);
 }
 
+// `delta_weight` (d floats; null: none): the update is normalised on its way into the stream,
+// residual += delta * factor(delta_kind, delta_eps)(sum of squares of delta) * delta_weight.
 TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const float* scale, float eps_value,
-                            int kind, void* out, int n, int d, cudaStream_t stream) {
+                            int kind, void* out, int n, int d, const float* delta_weight, float delta_eps,
+                            int delta_kind, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
-    if (kind < TIS_NORM_L2_EPS || kind > TIS_NORM_MEAN_EPS) {
-        tis_set_error("add_rmsnorm: norm kind %d", kind);
+    if (kind < TIS_NORM_L2_EPS || kind > TIS_NORM_MEAN_EPS || delta_kind < TIS_NORM_L2_EPS || delta_kind > TIS_NORM_MEAN_EPS) {
+        tis_set_error("add_rmsnorm: norm kinds %d, %d", kind, delta_kind);
         return TIS_BAD_SIZE;
     }
     const NormFactor eps = norm_factor(kind, d, eps_value);
+    const NormFactor dfac = norm_factor(delta_kind, d, delta_eps);
+    const float* dw = delta != nullptr ? delta_weight : nullptr;
     if ((size_t)d * sizeof(float) > 96 * 1024) {
         tis_set_error("add_rmsnorm: width %d too large (one row must fit 96 KB of shared memory)", d);
         return TIS_BAD_SIZE;
@@ -185,10 +243,10 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
         const int chunks = (d + 32 * per_lane - 1) / (32 * per_lane);
         if (d % per_lane == 0 && chunks <= 8) {
             TIS_DISPATCH_DTYPE(dtype, T, {
-                if (chunks <= 2) launch_add_rmsnorm_rows<T, 2>(residual, (const T*)delta, scale, eps, (T*)out, n, d, stream);
-                else if (chunks <= 4) launch_add_rmsnorm_rows<T, 4>(residual, (const T*)delta, scale, eps, (T*)out, n, d, stream);
-                else if (chunks <= 6) launch_add_rmsnorm_rows<T, 6>(residual, (const T*)delta, scale, eps, (T*)out, n, d, stream);
-                else launch_add_rmsnorm_rows<T, 8>(residual, (const T*)delta, scale, eps, (T*)out, n, d, stream);
+                if (chunks <= 2) launch_add_rmsnorm_rows<T, 2>(residual, (const T*)delta, scale, eps, (T*)out, n, d, dw, dfac, stream);
+                else if (chunks <= 4) launch_add_rmsnorm_rows<T, 4>(residual, (const T*)delta, scale, eps, (T*)out, n, d, dw, dfac, stream);
+                else if (chunks <= 6) launch_add_rmsnorm_rows<T, 6>(residual, (const T*)delta, scale, eps, (T*)out, n, d, dw, dfac, stream);
+                else launch_add_rmsnorm_rows<T, 8>(residual, (const T*)delta, scale, eps, (T*)out, n, d, dw, dfac, stream);
             });
             return tis_check_launch("add_rmsnorm");
         }
@@ -199,7 +257,7 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tis_launch(add_rmsnorm_kernel<T>, dim3(n), dim3(threads), smem, stream, residual, (const T*)delta, scale, eps,
-                   (T*)out, d);
+                   (T*)out, d, dw, dfac);
     });
     return tis_check_launch("add_rmsnorm");
 }
@@ -617,6 +675,99 @@ TIS_API int tis_scale_f32(float* x, float scale, size_t total, cudaStream_t stre
     if (blocks > 148 * 16) blocks = 148 * 16;
     tis_launch(scale_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, scale, total);
     return tis_check_launch("scale_f32");
+}
+
+// ----------------------------------------------------------------------------------
+// x = cap * tanh(x / cap) over `total` floats (logits that are bounded smoothly by +-cap)
+// ----------------------------------------------------------------------------------
+__global__ void softcap_f32_kernel(float* __restrict__ x, float cap, float inv_cap, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] * inv_cap);
+}
+
+TIS_API int tis_softcap_f32(float* x, float cap, size_t total, cudaStream_t stream) {
+    if (total == 0) return TIS_OK;
+    if (!(cap > 0.f)) {
+        tis_set_error("softcap: the bound must be positive, got %g", (double)cap);
+        return TIS_BAD_SIZE;
+    }
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    tis_launch(softcap_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, cap, 1.f / cap, total);
+    return tis_check_launch("softcap_f32");
+}
+
+// ----------------------------------------------------------------------------------
+// out = act(x) element by element over (n, F), rows of x and out with strides of their own.
+// kind 0: relu(x)^2; 1: gelu in its tanh form, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))); 2: silu.
+// ----------------------------------------------------------------------------------
+enum { TIS_ACT_RELU2 = 0, TIS_ACT_GELU_TANH = 1, TIS_ACT_SILU = 2 };
+
+__device__ __forceinline__ float activation_f(float x, int kind) {
+    if (kind == TIS_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == TIS_ACT_GELU_TANH) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.f + expf(-x));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out, int ldo, int F, int kind,
+                                  size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / F;
+        const int j = (int)(idx - r * F);
+        out[r * ldo + j] = from_f32<T>(activation_f(to_f32(x[r * ldx + j]), kind));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+activation_vec_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out, int ldo, int F, int kind, size_t total) {
+    constexpr int N = Vec16<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = F / N;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / per_row;
+        const int j = (int)(idx - r * per_row) * N;
+        float v[N];
+        Vec16<T>::load(x + r * ldx + j, v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v[e] = activation_f(v[e], kind);
+        Vec16<T>::store(out + r * ldo + j, v);
+    }
+}
+
+TIS_API int tis_activation(int dtype, const void* x, int ldx, void* out, int ldo, int n, int F, int kind,
+                           cudaStream_t stream) {
+    if (n <= 0 || F <= 0) return TIS_OK;
+    if (kind < TIS_ACT_RELU2 || kind > TIS_ACT_SILU || ldx < F || ldo < F) {
+        tis_set_error("activation: kind %d, %d columns, row lengths %d in and %d out", kind, F, ldx, ldo);
+        return TIS_BAD_SIZE;
+    }
+    const int per = dtype == TIS_BF16 ? 8 : 4;
+    if (F % per == 0 && ldx % per == 0 && ldo % per == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+        const size_t total = (size_t)n * (F / per);
+        size_t blocks = (total + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        TIS_DISPATCH_DTYPE(dtype, T,
+            tis_launch(activation_vec_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)x, ldx, (T*)out, ldo,
+                       F, kind, total));
+        return tis_check_launch("activation");
+    }
+    const size_t total = (size_t)n * F;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(activation_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)x, ldx, (T*)out, ldo, F,
+                   kind, total));
+    return tis_check_launch("activation");
 }
 
 // ----------------------------------------------------------------------------------

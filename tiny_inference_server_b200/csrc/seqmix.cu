@@ -389,9 +389,147 @@ TIS_API int tis_norm_mix_store(int dtype, void* qkv, int ld, int nq, int nk, int
 }
 
 // ------------------------------------------------------------------------------------------------------------
+// Between the projections and the cache of attention whose heads carry several score maps over the same values.
+// A row of `qkv` holds H * M query runs, G * M key runs (`dim` elements each: head by head, map by map) and G value
+// runs of `vdim` elements.  `bias` (all of these, in the row's order; null: none) is added first.  Every query and key
+// run is divided by its root mean square (eps inside the root) and multiplied by wq / wk (`dim` weights, the same for
+// every run; null: left as it is).  Queries are then multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1)
+// (every <= 0: not).  Keys and values go to the row's page: a key row of a kv head is its M runs side by side.
+// Queries go to q_out as H * M query heads of the key row's whole width M * dim: run (h, m) fills the m-th stretch
+// of `dim` elements of head h * M + m and the other stretches are zero, so that a product with a key row meets only
+// the key's run of the same map.  A CTA a row, a warp a run.
+// ------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_store_kernel(const T* __restrict__ qkv, int ld, int H, int G, int M, int dim, int vdim,
+                       const float* __restrict__ bias, const float* __restrict__ wq, const float* __restrict__ wk,
+                       float eps, float temp_coef, int temp_every, T* __restrict__ q_out, int ldq,
+                       T* __restrict__ k_pages, size_t k_page_stride, size_t k_head_stride, T* __restrict__ v_pages,
+                       size_t v_page_stride, size_t v_head_stride, int page_size, int num_pages,
+                       const int* __restrict__ block_table, int bt_stride, const int* __restrict__ positions,
+                       const int* __restrict__ row_slot, int* __restrict__ fault) {
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (pos < 0 || page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicExch(fault, 7);
+        return;
+    }
+    const float temp = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
+    const int in_page = pos % page_size;
+    const int q_runs = H * M, k_runs = G * M, kw = M * dim;
+    pdl_wait();
+    const T* row = qkv + (size_t)r * ld;
+    for (int run = warp; run < q_runs + k_runs; run += nwarps) {
+        const bool is_q = run < q_runs;
+        const int at = run * dim;                       // queries first, keys behind them: runs are contiguous
+        const float* w = is_q ? wq : wk;
+        float ss = 0.f;
+        for (int i = lane; i < dim; i += 32) {
+            const float v = to_f32(row[at + i]) + (bias != nullptr ? bias[at + i] : 0.f);
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        float f = w != nullptr ? rsqrtf(ss / (float)dim + eps) : 1.f;
+        if (is_q) f *= temp;
+        const int m = run % M;
+        if (is_q) {
+            T* dst = q_out + (size_t)r * ldq + (size_t)run * kw;
+            for (int i = lane; i < kw; i += 32) {
+                const int e = i - m * dim;
+                float v = 0.f;
+                if (e >= 0 && e < dim)
+                    v = (to_f32(row[at + e]) + (bias != nullptr ? bias[at + e] : 0.f)) * f * (w != nullptr ? w[e] : 1.f);
+                dst[i] = from_f32<T>(v);
+            }
+        } else {
+            const int kvh = (run - q_runs) / M;
+            T* dst = k_pages + (size_t)page * k_page_stride + (size_t)kvh * k_head_stride + (size_t)in_page * kw + m * dim;
+            for (int i = lane; i < dim; i += 32) {
+                const float v = (to_f32(row[at + i]) + (bias != nullptr ? bias[at + i] : 0.f)) * f * (w != nullptr ? w[i] : 1.f);
+                dst[i] = from_f32<T>(v);
+            }
+        }
+    }
+    const int v_at = (q_runs + k_runs) * dim;
+    for (int i = threadIdx.x; i < G * vdim; i += blockDim.x) {
+        const int kvh = i / vdim, e = i - kvh * vdim;
+        const float v = to_f32(row[v_at + i]) + (bias != nullptr ? bias[v_at + i] : 0.f);
+        v_pages[(size_t)page * v_page_stride + (size_t)kvh * v_head_stride + (size_t)in_page * vdim + e] = from_f32<T>(v);
+    }
+}
+
+TIS_API int tis_head_norm_store(int dtype, const void* qkv, int ld, int H, int G, int M, int dim, int vdim,
+                                const float* bias, const float* wq, const float* wk, float eps, float temp_coef,
+                                int temp_every, void* q_out, int ldq, void* k_pages, size_t k_page_stride,
+                                size_t k_head_stride, void* v_pages, size_t v_page_stride, size_t v_head_stride,
+                                int page_size, int num_pages, const int* block_table, int bt_stride,
+                                const int* positions, const int* row_slot, int* fault, int n, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (H <= 0 || G <= 0 || M <= 0 || dim <= 0 || vdim <= 0 || page_size <= 0 || ld < ((H + G) * M * dim + G * vdim) ||
+        ldq < H * M * M * dim) {
+        tis_set_error("head_norm_store: %d query heads, %d kv heads, %d maps of %d elements, value width %d, page size %d, "
+                      "row lengths %d in and %d out", H, G, M, dim, vdim, page_size, ld, ldq);
+        return TIS_BAD_SIZE;
+    }
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(head_norm_store_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)qkv, ld, H, G, M, dim, vdim, bias,
+                   wq, wk, eps, temp_coef, temp_every, (T*)q_out, ldq, (T*)k_pages, k_page_stride, k_head_stride,
+                   (T*)v_pages, v_page_stride, v_head_stride, page_size, num_pages, block_table, bt_stride, positions,
+                   row_slot, fault));
+    return tis_check_launch("head_norm_store");
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Two score maps of a head combined: a row of `a` holds, head by head, the outputs of map 1 and of map 2 (`vdim`
+// elements each); out[r, h] = o / sqrt(mean(o^2) + eps) * out_scale with o = a1 - lambda * a2, in 32-bit.  A warp per
+// (row, head).
+// ------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const T* __restrict__ a, int lda, float lambda, float eps, float out_scale, T* __restrict__ out,
+                    int ldo, const int* __restrict__ row_slot, int n, int H, int vdim) {
+    pdl_launch_dependents();
+    const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (idx >= n * H) return;
+    const int r = idx / H, head = idx - r * H;
+    if (row_slot != nullptr && row_slot[r] < 0) return;
+    pdl_wait();
+    const T* a1 = a + (size_t)r * lda + (size_t)head * 2 * vdim;
+    const T* a2 = a1 + vdim;
+    float ss = 0.f;
+    for (int j = lane; j < vdim; j += 32) {
+        const float o = fmaf(-lambda, to_f32(a2[j]), to_f32(a1[j]));
+        ss = fmaf(o, o, ss);
+    }
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss / (float)vdim + eps) * out_scale;
+    for (int j = lane; j < vdim; j += 32)
+        out[(size_t)r * ldo + (size_t)head * vdim + j] = from_f32<T>(fmaf(-lambda, to_f32(a2[j]), to_f32(a1[j])) * f);
+}
+
+TIS_API int tis_diff_combine(int dtype, const void* a, int lda, float lambda, float eps, float out_scale, void* out,
+                             int ldo, const int* row_slot, int n, int H, int vdim, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (H <= 0 || vdim <= 0 || lda < 2 * H * vdim || ldo < H * vdim) {
+        tis_set_error("diff_combine: %d heads of %d values, row lengths %d in and %d out", H, vdim, lda, ldo);
+        return TIS_BAD_SIZE;
+    }
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(diff_combine_kernel<T>, dim3((n * H + 3) / 4), dim3(128), 0, stream, (const T*)a, lda, lambda, eps,
+                   out_scale, (T*)out, ldo, row_slot, n, H, vdim));
+    return tis_check_launch("diff_combine");
+}
+
+// ------------------------------------------------------------------------------------------------------------
 // Attention of one row and query head over the keys lo..pos of its request's pages, lo = max(0, pos - window + 1)
 // (window 0: lo = 0):  score_j = q . k_j * scale - r1[head] * ln(1 + r2[head] * (pos - j)), softmax, times values,
-// times sigmoid(gate) element by element.  r1 null: no bias; gate null: no gate.
+// times sigmoid(gate) element by element (gate_per_head: `gate` holds one number per head, for all its elements).
+// r1 null: no bias; gate null: no gate.
 // A CTA of 128 threads: 128 keys a tile, a thread a key for the scores; for the values the threads form
 // 128 / v_dim groups, each taking every groups-th key of the tile, a thread a value column.
 // ------------------------------------------------------------------------------------------------------------
@@ -406,7 +544,7 @@ window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         const int* __restrict__ block_table, int bt_stride, int num_pages,
                         const int* __restrict__ positions, const int* __restrict__ row_slot, int H, int G, int k_dim,
                         int v_dim, int page_size, int window, float scale, const float* __restrict__ r1,
-                        const float* __restrict__ r2, const float* __restrict__ sink, int v_row,
+                        const float* __restrict__ r2, const float* __restrict__ sink, int v_row, int gate_per_head,
                         int* __restrict__ fault) {
     extern __shared__ float smem[];
     __shared__ float red[33];
@@ -498,7 +636,8 @@ window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
             if (c < v_dim) {
                 float o = acc[a] * inv;
                 if (gate != nullptr) {
-                    const float gv = to_f32(gate[(size_t)r * ldg + (size_t)head * v_dim + c]);
+                    const float gv = to_f32(gate_per_head ? gate[(size_t)r * ldg + head]
+                                                          : gate[(size_t)r * ldg + (size_t)head * v_dim + c]);
                     o = o / (1.f + expf(-gv));
                 }
                 out[(size_t)r * ldo + (size_t)head * v_dim + c] = from_f32<T>(o);
@@ -512,7 +651,8 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
                                  size_t v_page_stride, size_t v_head_stride, const int* block_table, int bt_stride,
                                  int num_pages, const int* positions, const int* row_slot, int n, int H, int G,
                                  int k_dim, int v_dim, int page_size, int window, float scale, const float* r1,
-                                 const float* r2, const float* sink, int v_row, int* fault, cudaStream_t stream) {
+                                 const float* r2, const float* sink, int v_row, int gate_per_head, int* fault,
+                                 cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > WA_THREADS * WA_MAX_COLS || page_size <= 0 ||
         window < 0 || v_row < v_dim) {
@@ -526,7 +666,7 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
         tis_launch(window_attention_kernel<T>, dim3(n, H), dim3(WA_THREADS), smem, stream, (const T*)q, ldq,
                    (const T*)gate, ldg, (T*)out, ldo, (const T*)k_pages, k_page_stride, k_head_stride, (const T*)v_pages,
                    v_page_stride, v_head_stride, block_table, bt_stride, num_pages, positions, row_slot, H, G, k_dim,
-                   v_dim, page_size, window, scale, r1, r2, sink, v_row, fault));
+                   v_dim, page_size, window, scale, r1, r2, sink, v_row, gate_per_head, fault));
     return tis_check_launch("window_attention");
 }
 
@@ -553,7 +693,11 @@ __device__ __forceinline__ float gate_f(float x, int act) { const float s = 1.f 
 // where the decay of a token comes from: a projection per head and key channel, a projection per head, or a constant
 // per head (`A_log` then holds the constants themselves and the recurrence is plain linear attention: q, k and v pass
 // silu instead of the unit norms, and the state takes k v^T without the correction towards v)
-enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2 };
+// or (DECAY_FORGET_GATE) a forget gate per head and key channel that also decides what is written: with `a_in` the
+// gate's projection, `dt_bias` its bias and `A_log` a lower bound per head and key channel, f = low + (1 - low) *
+// sigmoid(a + bias), S <- diag(f) S + (1 - f) v^T, o = S^T silu(q): the key is 1 - f, there is no key projection (a
+// row of `qkv` holds the queries and then the values), no unit norms and no correction towards v
+enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2, DECAY_FORGET_GATE = 3 };
 
 template <typename T, int DIM>
 __global__ void __launch_bounds__(256)
@@ -581,7 +725,9 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     float* betas = os + DELTA_CHUNK * v_dim;            // [CHUNK]
     float* S_sh = betas + DELTA_CHUNK;                  // [k_dim][v_dim] when DIM == 0
     const bool plain = decay_mode == DECAY_CONSTANT;
-    const float decay_rate = plain ? A_log[head] : expf(A_log[head]);
+    const bool forget = decay_mode == DECAY_FORGET_GATE;
+    const bool corrects = !plain && !forget;            // the delta rule proper: the state is corrected towards v
+    const float decay_rate = plain ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * k_dim * v_dim;
     constexpr int REG = DIM > 0 ? DIM : 1;
     float S[REG];
@@ -594,12 +740,25 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
             for (int i = 0; i < k_dim; ++i) S_sh[i * v_dim + tid] = S_glob[(size_t)i * v_dim + tid];
         }
     }
-    const int q_off = kvh * k_dim, k_off = G * k_dim + kvh * k_dim, v_off = 2 * G * k_dim + head * v_dim;
+    const int q_off = kvh * k_dim, k_off = G * k_dim + kvh * k_dim, v_off = (forget ? 1 : 2) * G * k_dim + head * v_dim;
     for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
         const int cnt = min(DELTA_CHUNK, rows - c0);
         __syncthreads();                                // the chunk before is done with the shared arrays
         for (int t = warp; t < cnt; t += nwarps) {
             const T* row = qkv + (size_t)(r0 + c0 + t) * ld;
+            if (forget) {
+                const T* arow = a_in + (size_t)(r0 + c0 + t) * lda + (size_t)head * k_dim;
+                for (int i = lane; i < k_dim; i += 32) {
+                    const float low = A_log[head * k_dim + i];
+                    const float open = 1.f / (1.f + expf(to_f32(arow[i]) + dt_bias[head * k_dim + i]));   // 1 - sigmoid
+                    qs[t * k_dim + i] = silu_f(to_f32(row[q_off + i]));
+                    ks[t * k_dim + i] = (1.f - low) * open;                      // 1 - f
+                    gs[t * k_dim + i] = low + (1.f - low) * (1.f - open);        // f
+                }
+                for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = to_f32(row[v_off + j]);
+                if (lane == 0) betas[t] = 1.f;
+                continue;
+            }
             float sq = 0.f, sk = 0.f;
             for (int i = lane; i < k_dim; i += 32) {
                 const float qv = to_f32(row[q_off + i]), kv = to_f32(row[k_off + i]);
@@ -646,7 +805,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S[i] *= gt[i];
                         dot = fmaf(S[i], kt[i], dot);
                     }
-                    const float u = plain ? vs[t * v_dim + tid] : betas[t] * (vs[t * v_dim + tid] - dot);
+                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : vs[t * v_dim + tid];
 #pragma unroll
                     for (int i = 0; i < REG; ++i) {
                         S[i] = fmaf(kt[i], u, S[i]);
@@ -658,7 +817,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S_sh[i * v_dim + tid] = s;
                         dot = fmaf(s, kt[i], dot);
                     }
-                    const float u = plain ? vs[t * v_dim + tid] : betas[t] * (vs[t * v_dim + tid] - dot);
+                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : vs[t * v_dim + tid];
                     for (int i = 0; i < k_dim; ++i) {
                         const float s = fmaf(kt[i], u, S_sh[i * v_dim + tid]);
                         S_sh[i * v_dim + tid] = s;
@@ -708,7 +867,9 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
 // a column read different banks with 16-byte loads.  A chunk is prepared by all threads, NT / 16 to a token; the raw
 // values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
 // unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
-template <typename T, int DL, int LANES, int COLS, bool PLAIN>
+// MODE 0: the delta rule (decays from projections, the state corrected towards v); 1: a constant decay per head,
+// silu on q, k and v, no correction; 2: the forget gate of DECAY_FORGET_GATE.
+template <typename T, int DL, int LANES, int COLS, int MODE>
 __global__ void __launch_bounds__(COLS * LANES)
 delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
                         int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
@@ -738,14 +899,14 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int col = tid / LANES, part = tid % LANES;
     // PLAIN: the decay is a constant per head and the state takes k v^T as it is, so the walk needs neither the decays of
     // the chunk nor the first of its two sums over the lanes of a column
-    constexpr bool plain = PLAIN;
-    const float decay_rate = plain ? A_log[head] : expf(A_log[head]);
+    constexpr bool plain = MODE == 1, forget = MODE == 2;
+    const float decay_rate = plain ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
     float S[DL];
     pdl_wait();
 #pragma unroll
     for (int i = 0; i < DL; ++i) S[i] = S_glob[(size_t)(part * DL + i) * v_dim];
-    const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = 2 * G * KDIM + head * v_dim + col0;
+    const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = (forget ? 1 : 2) * G * KDIM + head * v_dim + col0;
     const int nv = H * v_dim;
     const int pt = tid / PT, sub = tid % PT;
     const size_t a_at = decay_mode == DECAY_PER_HEAD ? (size_t)head : (size_t)head * KDIM;
@@ -758,16 +919,19 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
             rq[i] = live ? to_f32(row[q_off + sub * CH + i]) : 0.f;
-            rk[i] = live ? to_f32(row[k_off + sub * CH + i]) : 0.f;
+            rk[i] = (live && !forget) ? to_f32(row[k_off + sub * CH + i]) : 0.f;
             ra[i] = (live && !plain) ? to_f32(a_in[rr * lda + a_at + (sub * CH + i) * a_step]) : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < VPT; ++i) rv[i] = live ? to_f32(row[v_off + sub * VPT + i]) : 0.f;
-        rb = (live && sub == 0 && !plain) ? to_f32(b_in[rr * ldb + head]) : 0.f;
+        rb = (live && sub == 0 && !plain && !forget) ? to_f32(b_in[rr * ldb + head]) : 0.f;
     };
-    float bias[CH];
+    float bias[CH], low[CH];
 #pragma unroll
-    for (int i = 0; i < CH; ++i) bias[i] = plain ? 0.f : dt_bias[a_at + (sub * CH + i) * a_step];
+    for (int i = 0; i < CH; ++i) {
+        bias[i] = plain ? 0.f : dt_bias[a_at + (sub * CH + i) * a_step];
+        low[i] = forget ? A_log[a_at + sub * CH + i] : 0.f;
+    }
     fetch(0);
     for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
         const int cnt = min(DELTA_CHUNK, rows - c0);
@@ -786,9 +950,16 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             for (int i = 0; i < CH; ++i) {
                 const int ch = sub * CH + i;
                 const int at = ch + (ch / DL) * 4;
-                qs[pt][at] = plain ? silu_f(rq[i]) : rq[i] * fq;
-                ks[pt][at] = plain ? silu_f(rk[i]) : rk[i] * fk;
-                gs[pt][at] = plain ? decay_rate : expf(-decay_rate * softplus_f(ra[i] + bias[i]));
+                if (forget) {
+                    const float open = 1.f / (1.f + expf(ra[i] + bias[i]));     // 1 - sigmoid of the gate
+                    qs[pt][at] = silu_f(rq[i]);
+                    ks[pt][at] = (1.f - low[i]) * open;                          // 1 - f
+                    gs[pt][at] = low[i] + (1.f - low[i]) * (1.f - open);         // f
+                } else {
+                    qs[pt][at] = plain ? silu_f(rq[i]) : rq[i] * fq;
+                    ks[pt][at] = plain ? silu_f(rk[i]) : rk[i] * fk;
+                    gs[pt][at] = plain ? decay_rate : expf(-decay_rate * softplus_f(ra[i] + bias[i]));
+                }
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) vs[pt][sub * VPT + i] = plain ? silu_f(rv[i]) : rv[i];
@@ -835,6 +1006,9 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             if (plain) {
 #pragma unroll
                 for (int i = 0; i < DL; ++i) S[i] *= decay_rate;
+            } else if (forget) {
+#pragma unroll
+                for (int i = 0; i < DL / 2; ++i) { S[2 * i] *= gc[i].x; S[2 * i + 1] *= gc[i].y; }
             } else {
 #pragma unroll
                 for (int i = 0; i < DL / 2; ++i) {
@@ -938,11 +1112,15 @@ static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb,
                                    int H, int G, int v_dim, int decay_mode, int gate_act, cudaStream_t stream) {
     const dim3 grid(H, v_dim / COLS, seg_row0 != nullptr ? segments : n);
     if (decay_mode == DECAY_CONSTANT)
-        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, true>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 1>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+                   lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
+                   decay_mode);
+    else if (decay_mode == DECAY_FORGET_GATE)
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 2>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
                    lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
                    decay_mode);
     else
-        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, false>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 0>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
                    lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
                    decay_mode);
     int st = tis_check_launch("delta_rule");
@@ -996,7 +1174,7 @@ static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const voi
                                    int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, int decay_mode,
                                    int gate_act, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
-    if (decay_mode < DECAY_PER_CHANNEL || decay_mode > DECAY_CONSTANT || gate_act < 0 || gate_act > 1 ||
+    if (decay_mode < DECAY_PER_CHANNEL || decay_mode > DECAY_FORGET_GATE || gate_act < 0 || gate_act > 1 ||
         (decay_mode == DECAY_CONSTANT && o_raw == nullptr)) {
         tis_set_error("delta_rule: decay mode %d, gate activation %d%s", decay_mode, gate_act,
                       o_raw == nullptr ? ", no scratch for the outputs" : "");
@@ -1083,4 +1261,18 @@ TIS_API int tis_linear_attention(int dtype, const void* qkv, int ld, const void*
     return matrix_state_recurrence(dtype, qkv, ld, nullptr, 0, nullptr, 0, gate, ldg, decay, nullptr, norm_w, eps, 0.f, 1.f,
                                    state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, H, k_dim, v_dim, narrow,
                                    seg_row0, segments, DECAY_CONSTANT, 0, stream);
+}
+
+// The recurrence with a forget gate per head and key channel (DECAY_FORGET_GATE): a row of `qv` holds the queries of H
+// heads (k_dim each, before silu) and the values of H heads (v_dim each); `f_in` (n, H * k_dim) the gate's projection,
+// `f_bias` its bias, `lower` the gate's lower bounds (H * k_dim each).  Per head out = o / sqrt(mean(o^2) + eps) * norm_w
+// (v_dim weights, the same for every head).  `o_raw`: n * H * v_dim floats of scratch where tis_delta_rule_splits.
+TIS_API int tis_forget_gate_recurrence(int dtype, const void* qv, int ld, const void* f_in, int ldf, const float* lower,
+                                       const float* f_bias, const float* norm_w, float eps, float* state,
+                                       size_t state_stride, void* out, int ldo, float* o_raw, const int* row_slot,
+                                       const int* row_last, int n, int H, int k_dim, int v_dim, int narrow,
+                                       const int* seg_row0, int segments, cudaStream_t stream) {
+    return matrix_state_recurrence(dtype, qv, ld, nullptr, 0, f_in, ldf, nullptr, 0, lower, f_bias, norm_w, eps, 0.f, 1.f,
+                                   state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, H, k_dim, v_dim, narrow,
+                                   seg_row0, segments, DECAY_FORGET_GATE, 0, stream);
 }

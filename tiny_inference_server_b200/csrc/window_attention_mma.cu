@@ -58,6 +58,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 struct Params {
     const bf16* q; int ldq;
     const bf16* gate; int ldg;
+    int gate_per_head;       // `gate` holds one number per query head (for all its elements) instead of one per element
     bf16* out; int ldo;
     const bf16* k_pages; size_t k_page_stride, k_head_stride;
     const bf16* v_pages; size_t v_page_stride, v_head_stride;
@@ -333,7 +334,8 @@ window_attention_mma_kernel(const Params p) {
             float x = den > 0.f ? num / den : 0.f;
             const size_t row = (size_t)(row0 + mrow / gq);
             const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
-            if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
+            if (p.gate != nullptr)
+                x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + (p.gate_per_head ? (size_t)(kvh * gq + mrow % gq) : col)])));
             p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
         }
         return;
@@ -365,7 +367,11 @@ window_attention_mma_kernel(const Params p) {
         for (int n = 0; n < VD / 8; ++n) {
             const int c = n * 8 + 2 * t4;
             float x0 = o[n][2 * h] * inv, x1 = o[n][2 * h + 1] * inv;
-            if (p.gate != nullptr) {
+            if (p.gate != nullptr && p.gate_per_head) {
+                const float gh = 1.f / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + kvh * gq + mrow % gq])));
+                x0 *= gh;
+                x1 *= gh;
+            } else if (p.gate != nullptr) {
                 const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.ldg + col0 + c);
                 x0 = x0 / (1.f + __expf(-__bfloat162float(gv.x)));
                 x1 = x1 / (1.f + __expf(-__bfloat162float(gv.y)));
@@ -407,7 +413,8 @@ window_attention_merge_kernel(const Params p, int splits) {
         for (int s = 0; s < splits; ++s) num = fmaf(part[s * step + c], factor[s], num);
         float x = num * inv;
         const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
-        if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
+        if (p.gate != nullptr)
+            x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + (p.gate_per_head ? (size_t)(kvh * gq + mrow % gq) : col)])));
         p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
     }
 }
@@ -433,24 +440,25 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
                                      const int* block_table, int bt_stride, int num_pages, const int* positions,
                                      const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
                                      int H, int G, int page_size, int window, float scale, const float* r1,
-                                     const float* r2, int splits, float* partial, const float* sink, int v_row, int* fault,
-                                     cudaStream_t stream) {
+                                     const float* r2, int splits, float* partial, const float* sink, int v_row,
+                                     int gate_per_head, int* fault, cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
     if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) {
         tis_set_error("window_attention_mma: %d key splits%s", splits, splits > 1 ? " without scratch" : "");
         return TIS_BAD_SIZE;
     }
-    if (H <= 0 || G <= 0 || H % G || H / G > ROWS || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
+    if (H <= 0 || G <= 0 || H % G || H / G > ROWS || page_size <= 0 || window < 0 || ldq % 8 || (ldg % 2 && !gate_per_head) ||
+        ldo % 2 ||
         v_row < VD || v_row % 8 ||
         k_page_stride % 8 || k_head_stride % 8 || v_page_stride % 8 || v_head_stride % 8 ||
-        ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((uintptr_t)gate | (uintptr_t)out) % 4) {
+        ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((gate_per_head ? (uintptr_t)0 : (uintptr_t)gate) | (uintptr_t)out) % 4) {
         tis_set_error("window_attention_mma: %d query heads, %d kv heads, page size %d, window %d, row strides %d/%d/%d "
                       "or an operand that is not aligned", H, G, page_size, window, ldq, ldg, ldo);
         return TIS_BAD_SIZE;
     }
     Params p;
     p.q = (const bf16*)q; p.ldq = ldq;
-    p.gate = (const bf16*)gate; p.ldg = ldg;
+    p.gate = (const bf16*)gate; p.ldg = ldg; p.gate_per_head = gate_per_head;
     p.out = (bf16*)out; p.ldo = ldo;
     p.k_pages = (const bf16*)k_pages; p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride;
     p.v_pages = (const bf16*)v_pages; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;

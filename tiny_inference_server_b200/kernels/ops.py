@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 9
+ABI_VERSION = 10
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -522,15 +522,18 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, sca
     return out
 
 
-def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], scale: torch.Tensor, eps: float,
-                out: Optional[torch.Tensor], kind: str = "l2_eps") -> Optional[torch.Tensor]:
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], scale: Optional[torch.Tensor], eps: float,
+                out: Optional[torch.Tensor], kind: str = "l2_eps", delta_norm=None) -> Optional[torch.Tensor]:
     """residual += delta (when given), then out = residual * factor * scale with the row's factor of ``kind``
-    (``NORM_KINDS``): sqrt(d) / (||residual|| + eps), or 1 / sqrt(mean(residual^2) + eps)."""
+    (``NORM_KINDS``): sqrt(d) / (||residual|| + eps), or 1 / sqrt(mean(residual^2) + eps).  ``out`` None: only the
+    sum.  ``delta_norm = (weight (d,) float32, eps, kind)``: the update passes a norm of its own on its way into the
+    stream, ``residual += delta * factor(delta) * weight``, all in 32-bit."""
     lib = library()
     n, d = residual.shape
     ref = out if out is not None else delta
+    dw, deps, dkind = (None, 0.0, "l2_eps") if delta_norm is None or delta is None else delta_norm
     _check(lib.tis_add_rmsnorm(_dt(ref), _p(residual), _p(delta), _p(scale), _f(eps), NORM_KINDS[kind], _p(out), n, d,
-                               _stream()), lib)
+                               _p(dw), _f(deps), NORM_KINDS[dkind], _stream()), lib)
     return out
 
 
@@ -792,6 +795,34 @@ def scale_f32(x: torch.Tensor, scale: float) -> torch.Tensor:
     return x
 
 
+def softcap_f32(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place (contiguous float32)."""
+    lib = library()
+    _check(lib.tis_softcap_f32(_p(x), _f(cap), ctypes.c_size_t(x.numel()), _stream()), lib)
+    return x
+
+
+#: activations of a feed-forward without a gate
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x) element by element over (n, F) (row strides free): ``relu2`` the square of relu, ``gelu_tanh``
+    0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), ``silu``."""
+    lib = library()
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r}: known are {sorted(ACTIVATIONS)}")
+    n, f = x.shape
+    _check(lib.tis_activation(_dt(x), _p(x), x.stride(0), _p(out), out.stride(0), n, f, ACTIVATIONS[kind], _stream()), lib)
+    return out
+
+
+def gemm_act(a, w: torch.Tensor, kind: str) -> torch.Tensor:
+    """``act(a @ w)``: the product, then the activation kernel.  ``a`` may be ``ScaledRows``."""
+    h = gemm(a, w)
+    return activation(h, h, kind)
+
+
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
                 row_last: torch.Tensor, residual: bool = False, silu: bool = False) -> torch.Tensor:
     """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + sum_j weight[j, c] *
@@ -865,12 +896,13 @@ WINDOW_ATTENTION_MMA = os.environ.get("TIS_WINDOW_ATTENTION_MMA", "1") != "0"
 WINDOW_ATTENTION_CTAS = 2 * 148
 
 
-def window_attention_mma_usable(q: torch.Tensor, gate, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor) -> bool:
+def window_attention_mma_usable(q: torch.Tensor, gate, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                                gate_per_head: bool = False) -> bool:
     k_dim, v_dim = k_pages.shape[3], v_pages.shape[3]
     return (WINDOW_ATTENTION_MMA and v_pages.stride(2) % 8 == 0 and q.dtype == torch.bfloat16 and k_dim % 16 == 0 and v_dim % 16 == 0
             and 16 <= k_dim <= 256 and 16 <= v_dim <= 256 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
             and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
-            and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))
+            and (gate is None or gate_per_head or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))
             and all(s % 8 == 0 for s in (k_pages.stride(0), k_pages.stride(1), v_pages.stride(0), v_pages.stride(1)))
             and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0)
 
@@ -879,12 +911,13 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                      v_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
                      num_heads: int, page_size: int, window: Optional[int], scale: float,
                      bias_slope: Optional[torch.Tensor], bias_rate: Optional[torch.Tensor], fault: torch.Tensor,
-                     step=None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     step=None, sink: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> torch.Tensor:
     """Attention of the step's rows over the paged cache with keys and values of any widths:
     ``score = q . k * scale - bias_slope[h] * ln(1 + bias_rate[h] * distance)``, softmax over the keys
     ``max(0, p - window + 1) .. p``, the result times ``sigmoid(gate)`` element by element.  ``q`` (n, H * k_dim),
     ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free.  ``sink`` (H,) float32: the softmax's
-    denominator of head h also holds ``exp(sink[h])`` (unscaled; it has no value).  The value rows may be a slice of
+    denominator of head h also holds ``exp(sink[h])`` (unscaled; it has no value).  ``gate_per_head``: ``gate`` is (n, H),
+    one number per head for all of the head's elements.  The value rows may be a slice of
     wider rows (``v_pages`` with a row stride above its width, for instance the first elements of the key rows).
 
     float32, and widths that are not multiples of 16: a CUDA-core kernel, a CTA per row and head.  bfloat16 inside
@@ -895,7 +928,8 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     kps, khs = _page_strides(k_pages, k_dim)
     vps, vhs, v_row = _page_strides(v_pages, v_dim, free_rows=True)
-    if step is not None and num_heads // kv_heads <= 64 and window_attention_mma_usable(q, gate, out, k_pages, v_pages):
+    if step is not None and num_heads // kv_heads <= 64 and window_attention_mma_usable(q, gate, out, k_pages, v_pages,
+                                                                                          gate_per_head):
         from . import window_plan
         row0, rows, count = step.plan(window_plan.planner(num_heads // kv_heads))
         wlib = window_attention_library(k_dim, v_dim)
@@ -918,14 +952,14 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                                              _p(block_table), block_table.stride(0), k_pages.shape[0], _p(positions),
                                              _p(row_slot), _p(row0), _p(rows), count, num_heads, kv_heads, page_size,
                                              int(window or 0), _f(scale), _p(bias_slope), _p(bias_rate), splits, _p(partial),
-                                             _p(sink), v_row, _p(fault), _stream()), wlib)
+                                             _p(sink), v_row, int(gate_per_head), _p(fault), _stream()), wlib)
         return out
     calls["window_attention"] += 1
     _check(lib.tis_window_attention(_dt(q), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                     _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs, _p(block_table),
                                     block_table.stride(0), k_pages.shape[0], _p(positions), _p(row_slot), n, num_heads,
                                     kv_heads, k_dim, v_dim, page_size, int(window or 0), _f(scale), _p(bias_slope),
-                                    _p(bias_rate), _p(sink), v_row, _p(fault), _stream()), lib)
+                                    _p(bias_rate), _p(sink), v_row, int(gate_per_head), _p(fault), _stream()), lib)
     return out
 
 
@@ -994,6 +1028,70 @@ def linear_attention(qkv: torch.Tensor, gate: Optional[torch.Tensor], decay: tor
     return out
 
 
+def forget_gate_recurrence(qv: torch.Tensor, f_in: torch.Tensor, lower: torch.Tensor, f_bias: torch.Tensor,
+                           norm_weight: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor,
+                           row_slot: torch.Tensor, row_last: torch.Tensor, num_heads: int, k_dim: int, v_dim: int,
+                           requests: Optional[int] = None, segments=None) -> torch.Tensor:
+    """A matrix state per head whose forget gate, per key channel, also is one minus the key, over the rows of every
+    request, from and into ``state`` (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of
+    ``qv``: queries of H heads (k_dim each, before silu), values of H heads (v_dim each); ``f_in`` (n, H * k_dim) the
+    gate's projection.  ``f = lower + (1 - lower) * sigmoid(f_in + f_bias)``; ``S <- diag(f) S + (1 - f) v^T``;
+    ``o = S^T silu(q)``; per head ``out = o / rms(o) * norm_weight`` (v_dim weights shared by the heads).  Gate, state
+    and norm are 32-bit.  ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
+    lib = library()
+    n = qv.shape[0]
+    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    raw = None
+    if lib.tis_delta_rule_splits(k_dim, v_dim):
+        raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qv.device)
+        global launches
+        launches += 1
+    _check(lib.tis_forget_gate_recurrence(_dt(qv), _p(qv), qv.stride(0), _p(f_in), f_in.stride(0), _p(lower), _p(f_bias),
+                                          _p(norm_weight), _f(eps), _p(state), ctypes.c_size_t(state.stride(0)), _p(out),
+                                          out.stride(0), _p(raw), _p(row_slot), _p(row_last), n, num_heads, k_dim, v_dim,
+                                          int(narrow), _p(segments[0] if segments is not None else None),
+                                          int(segments[1]) if segments is not None else 0, _stream()), lib)
+    return out
+
+
+def head_norm_store(qkv: torch.Tensor, num_heads: int, kv_heads: int, maps: int, dim: int, v_dim: int,
+                    bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                    eps: float, temp_coef: float, temp_every: int, q_out: torch.Tensor, k_pages: torch.Tensor,
+                    v_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
+                    page_size: int, fault: torch.Tensor) -> None:
+    """Between the projections and the cache of attention whose heads carry ``maps`` score maps over the same values.
+    A row of ``qkv``: ``num_heads * maps`` query runs, ``kv_heads * maps`` key runs (``dim`` elements each, head by
+    head, map by map), ``kv_heads`` value runs of ``v_dim``.  ``bias`` (float32, the row's layout; None: none) is
+    added; every query and key run is divided by its root mean square (eps inside the root) and multiplied by
+    ``q_weight`` / ``k_weight`` (``dim`` weights shared by all runs; None: left alone); queries are multiplied by
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)`` at position p (``temp_every`` 0: not).  Keys (a kv head's
+    runs side by side: ``maps * dim`` wide) and values go to the row's place in ``k_pages`` / ``v_pages``.  ``q_out``
+    (n, H * maps * maps * dim) gets ``H * maps`` query heads as wide as a key row: run (h, m) in stretch m of head
+    ``h * maps + m``, zeros in its other stretches, so that it meets only map m's part of a key row."""
+    lib = library()
+    n = qkv.shape[0]
+    kps, khs = _page_strides(k_pages, maps * dim)
+    vps, vhs = _page_strides(v_pages, v_dim)
+    if k_pages.shape[1] != kv_heads or v_pages.shape[1] != kv_heads or q_out.stride(1) != 1 or qkv.stride(1) != 1:
+        raise KernelError("head_norm_store: the pages or the rows do not fit the sizes")
+    _check(lib.tis_head_norm_store(_dt(qkv), _p(qkv), qkv.stride(0), num_heads, kv_heads, maps, dim, v_dim, _p(bias),
+                                   _p(q_weight), _p(k_weight), _f(eps), _f(temp_coef), int(temp_every), _p(q_out),
+                                   q_out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs, page_size,
+                                   k_pages.shape[0], _p(block_table), block_table.stride(0), _p(positions), _p(row_slot),
+                                   _p(fault), n, _stream()), lib)
+
+
+def diff_combine(a: torch.Tensor, lam: float, eps: float, out_scale: float, out: torch.Tensor, num_heads: int,
+                 v_dim: int, row_slot: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Two score maps of a head combined: a row of ``a`` holds, head by head, map 1's and map 2's outputs (``v_dim``
+    each); ``out[r, h] = o / sqrt(mean(o^2) + eps) * out_scale`` with ``o = a1 - lam * a2``, in 32-bit."""
+    lib = library()
+    n = a.shape[0]
+    _check(lib.tis_diff_combine(_dt(a), _p(a), a.stride(0), _f(lam), _f(eps), _f(out_scale), _p(out), out.stride(0),
+                                _p(row_slot), n, num_heads, v_dim, _stream()), lib)
+    return out
+
+
 def latent_prepare(proj: torch.Tensor, dkv_at: int, num_heads: int, flat_dim: int, rot_dim: int, rank: int,
                    c_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, q_out: torch.Tensor,
                    k_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
@@ -1008,11 +1106,12 @@ def latent_prepare(proj: torch.Tensor, dkv_at: int, num_heads: int, flat_dim: in
     the caller fills.  Everything is computed in 32-bit."""
     lib = library()
     n = proj.shape[0]
-    if k_pages.shape[1] != 1 or k_pages.shape[3] != rank + rot_dim or cos.shape[1] * 2 > rot_dim:
+    dims = 0 if cos is None else 2 * cos.shape[1]          # no tables: nothing is rotated (a model without a rotated slice)
+    if k_pages.shape[1] != 1 or k_pages.shape[3] != rank + rot_dim or dims > rot_dim:
         raise KernelError("latent_prepare: the cache rows or the rotation tables do not fit the sizes")
     kps, _ = _page_strides(k_pages, rank + rot_dim)
     _check(lib.tis_latent_prepare(_dt(proj), _p(proj), proj.stride(0), dkv_at, num_heads, flat_dim, rot_dim,
-                                  2 * cos.shape[1], rank, _p(c_weight), _f(eps), _p(cos), _p(sin), cos.shape[0], _p(q_out), q_out.stride(0),
+                                  dims, rank, _p(c_weight), _f(eps), _p(cos), _p(sin), cos.shape[0] if cos is not None else 0, _p(q_out), q_out.stride(0),
                                   _p(k_pages), kps, page_size, k_pages.shape[0], _p(block_table), block_table.stride(0),
                                   _p(positions), _p(row_slot), _p(fault), n, _stream()), lib)
 

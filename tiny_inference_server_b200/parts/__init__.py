@@ -3,15 +3,17 @@ their arrangement in a block, embedding and output head."""
 from .base import (BuildContext, FeedForward, KVSpec, LayerBinding, Mixer, Norm, Part, PositionEncoding,
                    StateSpec, WeightSpec)
 from .stream import ResidualStream
-from .norms import RMSNormL2, RMSNormMeanEps, RMSNormOnePlus
+from .norms import RMSNormL2, RMSNormMeanEps, RMSNormOnePlus, RMSNormScalar
 from .positions import RotaryHalf, RotaryInterleaved, RotaryRescaled
 from .attention import GqaAttention
-from .feed_forward import ClampedGLU, RoutedExperts, SwiGLU
+from .feed_forward import ActMLP, ClampedGLU, RoutedExperts, SwiGLU
 from .short_conv import CausalConv
 from .window_attention import BiasedWindowAttention, ValueShare
 from .delta_rule import ChannelDeltaRule, HeadDecayDeltaRule
 from .linear_attention import DecayLinearAttention
 from .latent_attention import LatentAttention
+from .diff_attention import DifferentialAttention
+from .gated_recurrence import ForgetGateRecurrence
 from .block import Block
 from .embedding import Embedding, LMHead
 
@@ -19,4 +21,5 @@ __all__ = ["BuildContext", "FeedForward", "KVSpec", "LayerBinding", "Mixer", "No
            "PositionEncoding", "StateSpec", "WeightSpec", "ResidualStream", "RMSNormL2", "RMSNormMeanEps", "RMSNormOnePlus", "ClampedGLU", "CausalConv",
            "BiasedWindowAttention", "ValueShare", "ChannelDeltaRule", "HeadDecayDeltaRule", "DecayLinearAttention", "LatentAttention", "RoutedExperts",
            "RotaryRescaled", "RotaryHalf",
-           "RotaryInterleaved", "GqaAttention", "SwiGLU", "Block", "Embedding", "LMHead"]
+           "RotaryInterleaved", "GqaAttention", "SwiGLU", "Block", "Embedding", "LMHead", "RMSNormScalar", "ActMLP",
+           "DifferentialAttention", "ForgetGateRecurrence"]

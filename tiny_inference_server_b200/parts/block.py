@@ -1,8 +1,9 @@
 """A pre-norm block: norm, mixer, residual; norm, feed-forward, residual
 (upstream ``Transformer_block``, main_models_new.py:139-152).  Two options that upstream's block does
 not have: an *input filter* between the first norm and the mixer (a part with ``forward(x, step, state)``,
-for instance a short convolution over time, with per-request state of its own), and no feed-forward
-at all (the block is its first sublayer only)."""
+for instance a short convolution over time, with per-request state of its own), no feed-forward
+at all (the block is its first sublayer only), and a norm *behind* a sublayer as well (``post_mixer_norm``,
+``post_ffn_norm``): ``x += post(sublayer(norm(x)))``, the update normalised in 32-bit on its way into the stream."""
 from __future__ import annotations
 
 from typing import Optional
@@ -12,8 +13,11 @@ from .stream import ResidualStream
 
 
 class Block(Part):
-    def __init__(self, norm_mixer, mixer, norm_ffn, ffn, prefix: str = "", input_filter=None):
+    def __init__(self, norm_mixer, mixer, norm_ffn, ffn, prefix: str = "", input_filter=None, post_mixer_norm=None,
+                 post_ffn_norm=None):
         super().__init__(prefix)
+        self.post_mixer_norm = post_mixer_norm
+        self.post_ffn_norm = post_ffn_norm
         self.norm_mixer = norm_mixer
         self.mixer = mixer
         self.norm_ffn = norm_ffn
@@ -21,7 +25,8 @@ class Block(Part):
         self.input_filter = input_filter
 
     def children(self):
-        return tuple(p for p in (self.norm_mixer, self.input_filter, self.mixer, self.norm_ffn, self.ffn) if p is not None)
+        return tuple(p for p in (self.norm_mixer, self.input_filter, self.mixer, self.post_mixer_norm, self.norm_ffn,
+                                 self.ffn, self.post_ffn_norm) if p is not None)
 
     def filter_state_spec(self):
         return self.input_filter.state_spec() if self.input_filter is not None else None
@@ -30,6 +35,16 @@ class Block(Part):
         """``following``: the block that reads the stream after this one, if the caller knows it; its first
         norm can then be folded into this block's last product and that block's first one."""
         mixer, ffn = self.mixer, self.ffn
+        if self.post_mixer_norm is not None or self.post_ffn_norm is not None:
+            # an update that passes a norm cannot be added by the product that makes it (the norm needs whole rows):
+            # the norm behind a sublayer, the sum and the norm in front of the next sublayer are one kernel instead
+            a = stream.normed(self.norm_mixer)
+            if self.input_filter is not None:
+                a = self.input_filter.forward(a, step, binding.filter_state)
+            stream.add(mixer.forward(a, step, binding), post=self.post_mixer_norm)
+            if ffn is not None:
+                stream.add(ffn.forward(stream.normed(self.norm_ffn), step), post=self.post_ffn_norm)
+            return
         if self.input_filter is not None or ffn is None:
             # the mixer reads the filter's output, whole rows; the norm before the feed-forward can still be folded
             # into the mixer's last product and the feed-forward's first one

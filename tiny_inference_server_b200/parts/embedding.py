@@ -36,12 +36,14 @@ class Embedding(Part):
 class LMHead(Part):
     """``logits = h @ E^T`` with the embedding matrix (tied, main_models_new.py:225-226) or
     with a matrix of its own, ``lm_head.weight (vocab, width)``.  Logits are float32; ``logit_scale``
-    multiplies them (the embedding's own scale plays no part here)."""
+    multiplies them (the embedding's own scale plays no part here); ``softcap`` c (None: none) then bounds them
+    smoothly, ``c * tanh(logits / c)``."""
 
     def __init__(self, vocab: int, width: int, embedding: Optional[Embedding], prefix: str = "",
-                 weight_name: str = "lm_head.weight", logit_scale: float = 1.0):
+                 weight_name: str = "lm_head.weight", logit_scale: float = 1.0, softcap: Optional[float] = None):
         super().__init__(prefix)
         self.logit_scale = float(logit_scale)
+        self.softcap = float(softcap) if softcap else None
         self.vocab = vocab
         self.width = width
         self.embedding = embedding            # given: tied
@@ -63,4 +65,6 @@ class LMHead(Part):
         logits = ops.gemm_f32_out(h, wt)
         if self.logit_scale != 1.0:
             ops.scale_f32(logits, self.logit_scale)
+        if self.softcap is not None:
+            ops.softcap_f32(logits, self.softcap)
         return logits

@@ -109,6 +109,34 @@ class ClampedGLU(FeedForward):
         return ops.gemm(y, self.w_down)
 
 
+class ActMLP(FeedForward):
+    """``W_down act(W_up h)``: two matrices and an activation, no gate, no biases.  ``act``: ``relu2`` (the square of
+    relu), ``gelu_tanh`` or ``silu`` (``kernels.ops.ACTIVATIONS``).  Weights stored ``(out, in)``, names ``up, down``."""
+
+    def __init__(self, width: int, hidden: int, act: str = "relu2", prefix: str = ""):
+        super().__init__(prefix)
+        if act not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {act!r}: known are {sorted(ops.ACTIVATIONS)}")
+        self.width, self.hidden, self.act = width, hidden, act
+        self.w_up = self.w_down = None
+
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int):
+        f = cfg.layers[layer_index]["mlp"]
+        return cls(cfg.hidden_size, f["ff"], f.get("act", "relu2"), prefix=prefix)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"up": WeightSpec((self.hidden, self.width)), "down": WeightSpec((self.width, self.hidden))}
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        p = self.prefix
+        self.w_up = tensors[p + "up"].to(device=ctx.device, dtype=ctx.dtype).t().contiguous()
+        self.w_down = tensors[p + "down"].to(device=ctx.device, dtype=ctx.dtype).t().contiguous()
+
+    def forward(self, x, step=None):
+        return ops.gemm(ops.gemm_act(x, self.w_up, self.act), self.w_down)
+
+
 class RoutedExperts(FeedForward):
     """A mixture of ``experts`` small gated units ``W_down (silu(W_gate h) * (W_up h))`` (no biases), of which every
     token uses ``top``:
@@ -186,3 +214,4 @@ class RoutedExperts(FeedForward):
 register_part("ffn", "swiglu", SwiGLU)
 register_part("ffn", "routed_experts", RoutedExperts)
 register_part("ffn", "clamped_glu", ClampedGLU)
+register_part("ffn", "act_mlp", ActMLP)

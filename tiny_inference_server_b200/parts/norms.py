@@ -34,12 +34,16 @@ class RMSNormL2(Norm):
         self.scale = tensors[self.prefix + self.weight_name].to(device=ctx.device, dtype=torch.float32).contiguous()
         self.out_dtype = ctx.dtype
 
-    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], delta_norm=None) -> torch.Tensor:
         out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
-        return ops.add_rmsnorm(residual, delta, self.scale, self.eps, out)
+        return ops.add_rmsnorm(residual, delta, self.scale, self.eps, out, delta_norm=delta_norm)
 
     def forward(self, residual: torch.Tensor) -> torch.Tensor:
         return self.add_norm(residual, None)
+
+    def as_delta_norm(self):
+        """(weight, eps, kind of factor): this norm applied to an update on its way into the stream."""
+        return (self.scale, self.eps, "l2_eps")
 
     def sink(self, values: torch.Tensor):
         # the factor of a row, sqrt(width) / (||row|| + eps), is what the products apply themselves
@@ -74,12 +78,16 @@ class RMSNormMeanEps(Norm):
         self.scale = (w + self.offset).contiguous()
         self.out_dtype = torch.float32 if self.keep_f32 else ctx.dtype
 
-    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], delta_norm=None) -> torch.Tensor:
         out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
-        return ops.add_rmsnorm(residual, delta, self.scale, self.eps, out, kind="mean_eps")
+        return ops.add_rmsnorm(residual, delta, self.scale, self.eps, out, kind="mean_eps", delta_norm=delta_norm)
 
     def forward(self, residual: torch.Tensor) -> torch.Tensor:
         return self.add_norm(residual, None)
+
+    def as_delta_norm(self):
+        """(weight, eps, kind of factor): this norm applied to an update on its way into the stream."""
+        return (self.scale, self.eps, "mean_eps")
 
     def sink(self, values: torch.Tensor):
         return ops.ResidualSink(values, self.scale, self.eps, norm=self, kind="mean_eps")
@@ -92,6 +100,20 @@ class RMSNormOnePlus(RMSNormMeanEps):
         super().__init__(width, eps, prefix=prefix, weight_name=weight_name, offset=1.0)
 
 
+class RMSNormScalar(RMSNormMeanEps):
+    """``x / sqrt(mean(x^2) + eps) * g`` with ONE number ``g`` for all coordinates (the tensor has no dimensions).  On
+    the device the number is spread over the width, so that the kernels of the other norms serve."""
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((), init="ones_normal")}
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        g = tensors[self.prefix + self.weight_name].to(device=ctx.device, dtype=torch.float32).reshape(())
+        self.scale = (g + self.offset).expand(self.width).contiguous()
+        self.out_dtype = torch.float32 if self.keep_f32 else ctx.dtype
+
+
 register_part("norm", "rmsnorm_l2", RMSNormL2)
 register_part("norm", "rmsnorm_mean_eps", RMSNormMeanEps)
 register_part("norm", "rmsnorm_one_plus", RMSNormOnePlus)
+register_part("norm", "rmsnorm_scalar", RMSNormScalar)

@@ -4,7 +4,10 @@ stream next (one fused kernel), which is where every pre-norm block wants it.
 
 A part whose last product can add to the stream itself is given a *sink* instead (``sink``); what it
 hands back is the next norm's output short of one factor per row (``kernels.ops.ScaledRows``), kept
-here until that norm asks for it."""
+here until that norm asks for it.
+
+An update may also pass a norm of its own on its way into the stream (``add(update, post=norm)``, a block with a norm
+behind each sublayer): the same fused kernel normalises the update, adds it and normalises the sum."""
 from __future__ import annotations
 
 from typing import Optional
@@ -19,6 +22,7 @@ class ResidualStream:
         assert values.dtype == torch.float32
         self.values = values
         self.pending: Optional[torch.Tensor] = None
+        self.pending_post = None                  # the norm that the pending update passes before it is added
         self.ready: Optional[ops.ScaledRows] = None
 
     def sink(self, norm, dtype: torch.dtype):
@@ -28,15 +32,27 @@ class ResidualStream:
             return None
         return norm.sink(self.values)
 
-    def add(self, update) -> None:
-        """``update``: a part's result, or the ``ScaledRows`` of a part that has added its result itself."""
+    def _settle(self) -> None:
+        """Add the pending update now, without a norm of the sum."""
+        if self.pending is None:
+            return
+        if self.pending_post is not None:
+            ops.add_rmsnorm(self.values, self.pending, None, 0.0, None, delta_norm=self.pending_post.as_delta_norm())
+        else:
+            ops.residual_add(self.values, self.pending)
+        self.pending = self.pending_post = None
+
+    def add(self, update, post=None) -> None:
+        """``update``: a part's result, or the ``ScaledRows`` of a part that has added its result itself.
+        ``post``: a norm (with ``as_delta_norm``) that the update passes before it is added."""
         if isinstance(update, ops.ScaledRows):
+            if post is not None:
+                raise ValueError("an update that has been added already cannot pass a norm")
             self.ready = update
             return
         self.ready = None
-        if self.pending is not None:
-            ops.residual_add(self.values, self.pending)
-        self.pending = update
+        self._settle()
+        self.pending, self.pending_post = update, post
 
     def normed(self, norm, scaled: bool = False):
         """norm(values + pending); the sum stays in ``values``.  ``scaled``: the reader takes ``ScaledRows``."""
@@ -46,11 +62,12 @@ class ResidualStream:
                 return ready if scaled else ready.dense()
             return norm.add_norm(self.values, None)        # made for another norm: the stream itself is whole
         delta, self.pending = self.pending, None
+        post, self.pending_post = self.pending_post, None
+        if post is not None:
+            return norm.add_norm(self.values, delta, delta_norm=post.as_delta_norm())
         return norm.add_norm(self.values, delta)
 
     def flush(self) -> torch.Tensor:
         self.ready = None
-        if self.pending is not None:
-            ops.residual_add(self.values, self.pending)
-            self.pending = None
+        self._settle()
         return self.values
