@@ -107,7 +107,8 @@ def differential_attention(u, W, p, m, eps, positions=None):
     k = k.repeat_interleave(H // G, dim=1)
     v = v.repeat_interleave(H // G, dim=1)
     s = torch.einsum("ihmd,jhmd->hmij", q, k) * m["scale"]
-    w = softmax_rows(s, causal(L))                                     # (H, 2, L, L)
+    mask = m.get("mask")                                               # a window, if the layer has one; else every j <= i
+    w = softmax_rows(s, banded(L, mask["size"]) if mask else causal(L))   # (H, 2, L, L)
     a = torch.einsum("hmij,jhd->imhd", w, v)                           # both maps read the same values
     lam = differential_lambda(W, p, m["diff"])
     o = rms(a[:, 0] - lam * a[:, 1], eps) * (1.0 - m["diff"])          # per head over vdim, no weight
