@@ -369,6 +369,77 @@ def compare_mizidra(args):
     return 0
 
 
+def biruvik_config(width, heads, kv_heads, ffn, vocab, layers, window=1024, rank=128):
+    """A Biruvik model with the layer sizes of a member of the GQA family: in turn a layer of differential attention
+    (two maps with keys of 64, so that a cache row of keys is 128 wide, values of 128), one of windowed attention over
+    ``rank`` compressed elements a token with a gate per head, and one of the recurrence whose forget gate writes (keys
+    and values of 128); every layer with an ungated feed-forward of 1.5 ffn hidden elements, which holds as many
+    weights as the gated one of ffn."""
+    diff = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.3, "scale": 64 ** -0.5,
+            "q_temp": {"coef": 0.3, "every": 64}}
+    latent = {"heads": heads, "dim": 64, "vdim": 128, "kv_rank": rank, "scale": 64 ** -0.5, "mask": {"size": window}}
+    forget = {"heads": heads, "dim": 128, "vdim": 128}
+    kinds = [("attention", diff), ("latent_attention", latent), ("hgrn2", forget)]
+    ff = {"kind": "dense", "ff": ffn * 3 // 2 // 64 * 64}
+    return dict(architecture="Biruvik", vocab=vocab, width=width, norm={"eps": 1e-6}, embedding={"scale": 1.0},
+                logit_softcap=30.0, max_context=8192,
+                layers=[{"type": kinds[i % 3][0], "mixer": dict(kinds[i % 3][1]), "mlp": dict(ff)} for i in range(layers)])
+
+
+def compare_biruvik(args):
+    """``--compare biruvik``: prefill and decode of the Biruvik architecture beside the Mizidra architecture (the closest
+    earlier one: attention over compressed keys and values beside recurrent layers with a matrix state), the Kefisun
+    architecture and the rotary GQA model at equal layer sizes, and its kernels beside the like kernels of those.  One
+    JSON line; the default run is untouched."""
+    import gc
+    import types
+    import torch
+    from tiny_inference_server_b200.kernels import microbench, ops
+    from tiny_inference_server_b200.sampling import Sampler
+    pk = peaks()
+    count_ops = lambda: ops.launches  # noqa: E731
+    window, ctx, layers = 1024, 4096, 9
+    result = {"compare": "biruvik", "dtype": "bf16", "data": "synthetic", "layers": layers, "context": ctx, "window": window,
+              "peaks": pk, "sizes": {}}
+    for name in [x for x in args.compare_sizes.split(",") if x]:
+        base = SIZES[name][0]
+        twin = dict(base, num_layers=layers, num_mtp_heads=0, max_context=8192, tie_word_embeddings=True)
+        size = (base["hidden_size"], base["num_heads"], base["num_kv_heads"], base["ffn_hidden"], base["vocab_size"], layers)
+        point = {}
+        for label, cfg_dict in (("biruvik", biruvik_config(*size, window=window)), ("mizidra", mizidra_config(*size)),
+                                ("kefisun", kefisun_config(*size, window)), ("gqa", twin)):
+            runner = None
+            try:
+                _, runner = build_runner(cfg_dict, ctx, 8, mtp=False)
+                steps = max(8, args.steps // 2)
+                r = {}
+                for b in (1, 8):
+                    ms, launches = decode_run(runner, b, ctx - steps - args.warmup - 2, steps, args.warmup, Sampler, count_ops)
+                    r[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    r[f"decode_b{b}_ms"] = round(ms, 4)
+                    r[f"decode_b{b}_launches"] = round(launches, 1)
+                best, first = prefill_run(runner, PREFILL_TOKENS, reps=2)
+                r["prefill_tok_s"] = round(PREFILL_TOKENS / (best * 1e-3), 1)
+                r["prefill_ms"] = round(best, 3)
+                r["prefill_first_run_ms"] = round(first, 3)
+                point[label] = r
+            except Exception as e:                       # noqa: BLE001
+                point[label] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        margs = types.SimpleNamespace(width=base["hidden_size"], ffn=base["ffn_hidden"], heads=base["num_heads"],
+                                      kv_heads=base["num_kv_heads"], head_dim=128, page_size=PAGE, tokens=PREFILL_TOKENS, batch=8,
+                                      context=ctx, rank=128, window=window)
+        try:
+            point["kernels"] = microbench.differential_latent_forget(margs)
+        except Exception as e:                           # noqa: BLE001
+            point["kernels"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        result["sizes"][name] = point
+    print(json.dumps(result))
+    return 0
+
+
 def compare_kefisun(args):
     """``--compare kefisun``: prefill and decode of the Kefisun architecture beside the rotary GQA model at equal
     layer sizes (same width, heads, feed-forward, vocabulary, number of layers, and the same window of keys), and
@@ -514,7 +585,7 @@ def main(argv=None):
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, other contexts, MTP heads and prefill")
     ap.add_argument("--sizes", default="3b,8b", help="larger members of the family to measure too (3b, 8b; '' = none)")
-    ap.add_argument("--compare", default=None, choices=["kefisun", "mizidra"],
+    ap.add_argument("--compare", default=None, choices=["kefisun", "mizidra", "biruvik"],
                     help="instead of the default run: another architecture beside the GQA model at equal layer sizes")
     ap.add_argument("--compare-sizes", default="0.9b,3b", help="with --compare: whose layer sizes (0.9b, 3b, 8b)")
     args = ap.parse_args(argv)
@@ -526,6 +597,9 @@ def main(argv=None):
     if args.compare == "mizidra":
         args.warmup = max(args.warmup, 3)
         return compare_mizidra(args)
+    if args.compare == "biruvik":
+        args.warmup = max(args.warmup, 3)
+        return compare_biruvik(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -11,6 +11,9 @@
         convolution, delta rule and gating, each beside the like kernel of the rotary GQA model)
     python -m tiny_inference_server_b200.kernels.microbench latent-linear-routed   (attention over compressed keys
         and values, recurrences with a decay per head, routed experts, each beside the like kernel of an earlier model)
+    python -m tiny_inference_server_b200.kernels.microbench differential-latent-forget   (two score maps a head,
+        windowed attention over compressed rows with head gates, the recurrence whose forget gate writes, a norm behind a
+        sublayer, each beside the like kernel of an earlier model)
     python -m tiny_inference_server_b200.kernels.microbench all
 
 ``--reps N --no-timing`` launches the kernel N times and exits (a profiler attaches to that);
@@ -433,6 +436,153 @@ def latent_linear_routed(args):
     return out
 
 
+def differential_latent_forget(args):
+    """The kernels of differential attention (two score maps a head), of windowed attention over compressed keys and
+    values with a gate per head, of the recurrence whose forget gate also writes, of a norm behind a sublayer and of an
+    ungated activation, each beside the kernel of an earlier architecture of this engine that does the like work at
+    equal sizes (``None``: there is none).  Sizes: ``heads`` query and ``kv_heads`` key/value heads; a score map with
+    keys of ``head_dim / 2`` (a head's two maps together are ``head_dim`` wide) and values of ``head_dim``; ``rank``
+    compressed elements a token, seen through a window of ``window`` keys; the recurrence with keys and values of
+    ``head_dim``.  Returns {name: {us, rate, unit, like_us, like_rate}}."""
+    dev = "cuda"
+    d, F, H, G, hd, page = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, B, ctx, rank, W = args.tokens, args.batch, args.context, args.rank, args.window
+    dim = hd // 2
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    i32 = dict(device=dev, dtype=torch.int32)
+    fault = torch.zeros(4, **i32)
+    out = {}
+
+    def put(name, us, work, unit, like_us=None, like_work=None):
+        e = {"us": round(us, 2), "rate": round(work / us / 1e3, 1) if unit == "GB/s" else round(work / us / 1e6, 1), "unit": unit}
+        if like_us is not None:
+            lw = work if like_work is None else like_work
+            e["like_us"] = round(like_us, 2)
+            e["like_rate"] = round(lw / like_us / 1e3, 1) if unit == "GB/s" else round(lw / like_us / 1e6, 1)
+        out[name] = e
+        like = f"   like kernel {e['like_us']:9.2f} us {e['like_rate']:9.1f} {unit}" if like_us is not None else ""
+        print(f"{name:52s} {e['us']:9.2f} us {e['rate']:9.1f} {unit}{like}")
+
+    # ---- differential attention over a prompt portion of n rows from position 0: 2 H query heads as wide as a key row
+    # (two maps of dim), G kv heads; beside attention of H heads with keys and values of head_dim over the same cache.
+    # The work counted is the design's (two maps of dim against the keys, two sums of values), not the zeros the
+    # query rows carry where the other map's part of a key lies.
+    num_pages = (n + page - 1) // page
+    planes = [torch.randn(num_pages, 2, G, page, hd, **bf) for _ in range(2)]
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    pos, slot = torch.arange(n, **i32), torch.zeros(n, **i32)
+    last = torch.full((n,), n - 1, **i32)
+    q2 = torch.randn(n, 2 * H * hd, **bf)
+    maps = torch.empty(n, 2 * H * hd, **bf)
+    ql, ol = torch.randn(n, H * hd, **bf), torch.empty(n, H * hd, **bf)
+    step = _PortionStep(pos, slot)
+    pairs = n * (n + 1) // 2
+    t_new = _graph_time(lambda i: ops.window_attention(q2, None, maps, planes[i % 2][:, 0], planes[i % 2][:, 1], table, pos, slot,
+                                                       2 * H, page, None, dim ** -0.5, None, None, fault, step), 6)
+    t_like = _graph_time(lambda i: ops.window_attention(ql, None, ol, planes[i % 2][:, 0], planes[i % 2][:, 1], table, pos, slot,
+                                                        H, page, None, hd ** -0.5, None, None, fault, step), 6)
+    put(f"differential attention, {n} rows", t_new, 2.0 * 2 * H * (dim + hd) * pairs, "TFLOP/s", t_like, 4.0 * H * hd * pairs)
+    pages_per = (ctx + page - 1) // page
+    n_bufs = max(2, min(12, (300 << 20) // max(1, B * ctx * 2 * G * hd * 2)))
+    planes = [torch.randn(B * pages_per, 2, G, page, hd, **bf) for _ in range(n_bufs)]
+    dtable = torch.arange(B * pages_per, **i32).reshape(B, pages_per).contiguous()
+    pos_b, slot_b = torch.full((B,), ctx - 1, **i32), torch.arange(B, **i32)
+    dstep = _PortionStep(pos_b, slot_b, decode=True)
+    q2d, mapsd, qld, old = q2[:B].contiguous(), maps[:B].contiguous(), ql[:B].contiguous(), ol[:B].contiguous()
+    t_new = _graph_time(lambda i: ops.window_attention(q2d, None, mapsd, planes[i % n_bufs][:, 0], planes[i % n_bufs][:, 1], dtable,
+                                                       pos_b, slot_b, 2 * H, page, None, dim ** -0.5, None, None, fault, dstep))
+    t_like = _graph_time(lambda i: ops.window_attention(qld, None, old, planes[i % n_bufs][:, 0], planes[i % n_bufs][:, 1], dtable,
+                                                        pos_b, slot_b, H, page, None, hd ** -0.5, None, None, fault, dstep))
+    put(f"differential attention, {B} decode rows at {ctx}", t_new, B * ctx * 2 * G * hd * 2, "GB/s", t_like)
+    del planes
+    # ---- between the projections and the cache: bias, norm per head and map, temperature, cache write, padded queries
+    bufs = 4
+    plane = torch.zeros(num_pages, 2, G, page, hd, **bf)
+    nq, nk = H * hd, G * hd
+    qkv = [torch.randn(n, nq + 2 * nk, **bf) for _ in range(bufs)]
+    bias, qw, kw = torch.zeros(nq + 2 * nk, device=dev), torch.ones(dim, device=dev), torch.ones(dim, device=dev)
+    t_new = _graph_time(lambda i: ops.head_norm_store(qkv[i % bufs], H, G, 2, dim, hd, bias, qw, kw, 1e-6, 0.3, 64, q2, plane[:, 0],
+                                                      plane[:, 1], table, pos, slot, page, fault), 12)
+    wq, wk = torch.ones(nq, device=dev), torch.ones(nk, device=dev)
+    t_like = _graph_time(lambda i: ops.norm_mix_store(qkv[i % bufs], nq, nk, nk, wq, wk, 1e-6, None, None, plane[:, 0], plane[:, 1],
+                                                      table, pos, slot, page, fault), 12)
+    put(f"bias, norms, temperature, cache write, {n} rows", t_new, n * ((nq + 2 * nk) * 2 + 2 * nq + 2 * nk) * 2, "GB/s", t_like,
+        n * (nq + 2 * nk) * 2 * 2)
+    mp = [torch.randn(n, 2 * H * hd, **bf) for _ in range(bufs)]
+    t_new = _graph_time(lambda i: ops.diff_combine(mp[i % bufs], 0.8, 1e-6, 0.7, ol, H, hd, slot), 12)
+    res = [torch.randn(n, d, device=dev) for _ in range(bufs)]
+    delta = [torch.randn(n, d, **bf) for _ in range(bufs)]
+    normed, scale = torch.empty(n, d, **bf), torch.ones(d, device=dev)
+    t_plain = _graph_time(lambda i: ops.add_rmsnorm(res[i % bufs], delta[i % bufs], scale, 1e-6, normed), 12)
+    put(f"two maps combined and normed, {n} rows", t_new, n * 3 * H * hd * 2, "GB/s", t_plain, n * d * 12)
+    t_new = _graph_time(lambda i: ops.add_rmsnorm(res[i % bufs], delta[i % bufs], scale, 1e-6, normed, kind="mean_eps",
+                                                  delta_norm=(scale, 1e-6, "mean_eps")), 12)
+    put(f"normed update + sum + norm, {n} rows", t_new, n * d * 12, "GB/s", t_plain)
+    up = [torch.randn(n, 2 * F, **bf) for _ in range(bufs)]
+    hid = torch.empty(n, F, **bf)
+    t_new = _graph_time(lambda i: ops.activation(up[i % bufs][:, :F], hid, "relu2"), 12)
+    t_like = _graph_time(lambda i: ops.swiglu(up[i % bufs], hid, 32), 12)
+    put(f"squared relu, {n} rows", t_new, n * F * 4, "GB/s", t_like, n * F * 6)
+    # ---- windowed attention over compressed rows with a gate per head, beside the same cache without a window, with a
+    # rotated slice and a sink (the design this one's latent attention grew from)
+    rot = 64
+    cpages = [torch.randn(num_pages, 1, page, rank, **bf) for _ in range(2)]
+    rpages = [torch.randn(num_pages, 1, page, rank + rot, **bf) for _ in range(2)]
+    qc, qr = torch.randn(n, H * rank, **bf), torch.randn(n, H * (rank + rot), **bf)
+    lat, gates = torch.empty(n, H * rank, **bf), torch.randn(n, H, **bf)
+    sink = torch.zeros(H, device=dev)
+    seen = sum(min(p + 1, W) for p in range(n))
+    t_new = _graph_time(lambda i: ops.window_attention(qc, gates, lat, cpages[i % 2], cpages[i % 2][..., :rank], table, pos, slot, H,
+                                                       page, W, dim ** -0.5, None, None, fault, step, gate_per_head=True), 6)
+    t_like = _graph_time(lambda i: ops.window_attention(qr, None, lat, rpages[i % 2], rpages[i % 2][..., :rank], table, pos, slot, H,
+                                                        page, None, dim ** -0.5, None, None, fault, step, sink=sink), 6)
+    put(f"latent attention, window {W}, head gates, {n} rows", t_new, 4.0 * H * rank * seen, "TFLOP/s", t_like,
+        2.0 * H * (2 * rank + rot) * pairs)
+    n_bufs = max(2, min(12, (300 << 20) // max(1, B * ctx * (rank + rot) * 2)))
+    cpages = [torch.randn(B * pages_per, 1, page, rank, **bf) for _ in range(n_bufs)]
+    rpages = [torch.randn(B * pages_per, 1, page, rank + rot, **bf) for _ in range(n_bufs)]
+    qcd, qrd, latd, gd = qc[:B].contiguous(), qr[:B].contiguous(), lat[:B].contiguous(), gates[:B].contiguous()
+    t_new = _graph_time(lambda i: ops.window_attention(qcd, gd, latd, cpages[i % n_bufs], cpages[i % n_bufs][..., :rank], dtable, pos_b,
+                                                       slot_b, H, page, W, dim ** -0.5, None, None, fault, dstep, gate_per_head=True))
+    t_like = _graph_time(lambda i: ops.window_attention(qrd, None, latd, rpages[i % n_bufs], rpages[i % n_bufs][..., :rank], dtable,
+                                                        pos_b, slot_b, H, page, None, dim ** -0.5, None, None, fault, dstep, sink=sink))
+    put(f"latent attention, window {W}, {B} decode rows at {ctx}", t_new, B * min(W, ctx) * rank * 2, "GB/s", t_like,
+        B * ctx * (rank + rot) * 2)
+    del cpages, rpages
+    kp, kpr = torch.zeros(num_pages, 1, page, rank, **bf), torch.zeros(num_pages, 1, page, rank + rot, **bf)
+    proj = [torch.randn(n, H * (dim + rot) + rank + rot, **bf) for _ in range(bufs)]
+    cw = torch.ones(rank, device=dev)
+    cos, sin = torch.ones(n, rot // 2, device=dev), torch.zeros(n, rot // 2, device=dev)
+    t_new = _graph_time(lambda i: ops.latent_prepare(proj[i % bufs], H * dim, H, dim, 0, rank, cw, 1e-6, None, None, qc, kp, table,
+                                                     pos, slot, page, fault), 12)
+    t_like = _graph_time(lambda i: ops.latent_prepare(proj[i % bufs], H * (dim + rot), H, dim, rot, rank, cw, 1e-6, cos, sin, qr, kpr,
+                                                      table, pos, slot, page, fault), 12)
+    put(f"compressed vector normed into the cache, {n} rows", t_new, n * 2 * rank * 2, "GB/s", t_like,
+        n * (2 * H * rot + 2 * (rank + rot)) * 2)
+    # ---- the recurrence whose forget gate writes, beside linear attention with one decay per head
+    nv = H * hd
+    rows = [torch.randn(n, 3 * nv, **bf) for _ in range(2)]
+    lower, fb, nw, nwl = torch.rand(nv, device=dev) * 0.9, torch.zeros(nv, device=dev), torch.ones(hd, device=dev), torch.ones(nv, device=dev)
+    decay, gt = torch.full((H,), 0.97, device=dev), torch.randn(n, nv, **bf)
+    st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
+    od = torch.empty(n, nv, **bf)
+    one = (torch.zeros(1, **i32), 1)
+    t_new = _graph_time(lambda i: ops.forget_gate_recurrence(rows[i % 2][:, :2 * nv], rows[i % 2][:, 2 * nv:], lower, fb, nw, 1e-6, st, od,
+                                                             slot, last, H, hd, hd, requests=1, segments=one), 4)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.linear_attention(rows[i % 2], gt, decay, nwl, 1e-6, st, od, slot, last, H, hd, hd, requests=1,
+                                                        segments=one), 4)
+    put(f"forget-gate recurrence, {n} rows", t_new, 4.0 * n * H * hd * hd, "TFLOP/s", t_like)
+    st.zero_()
+    t_new = _graph_time(lambda i: ops.forget_gate_recurrence(rows[i % 2][:B, :2 * nv], rows[i % 2][:B, 2 * nv:], lower, fb, nw, 1e-6, st,
+                                                             od[:B], slot_b, slot_b, H, hd, hd, requests=B, segments=(slot_b, B)), 12)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.linear_attention(rows[i % 2][:B], gt[:B], decay, nwl, 1e-6, st, od[:B], slot_b, slot_b, H, hd, hd,
+                                                        requests=B, segments=(slot_b, B)), 12)
+    put(f"forget-gate recurrence, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s", t_like)
+    return out
+
+
 def sampling(args):
     """The sampling kernel at ``--rows`` rows of ``--vocab`` logits, for the kinds of setting a row can have."""
     dev = "cuda"
@@ -636,7 +786,7 @@ def timeline(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "sampling", "timeline",
-                                     "seqmix", "latent-linear-routed", "all"])
+                                     "seqmix", "latent-linear-routed", "differential-latent-forget", "all"])
     ap.add_argument("--rank", type=int, default=128, help="latent-linear-routed: compressed elements a token")
     ap.add_argument("--rot", type=int, default=64, help="latent-linear-routed: rotated elements a token")
     ap.add_argument("--experts", type=int, default=16)
@@ -685,6 +835,8 @@ def main(argv=None):
         seqmix(args)
     if args.what in ("latent-linear-routed", "all"):
         latent_linear_routed(args)
+    if args.what in ("differential-latent-forget", "all"):
+        differential_latent_forget(args)
     return 0
 
 
