@@ -375,14 +375,14 @@ def biruvik_config(width, heads, kv_heads, ffn, vocab, layers, window=1024, rank
     ``rank`` compressed elements a token with a gate per head, and one of the recurrence whose forget gate writes (keys
     and values of 128); every layer with an ungated feed-forward of 1.5 ffn hidden elements, which holds as many
     weights as the gated one of ffn."""
-    diff = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.3, "scale": 64 ** -0.5,
-            "q_temp": {"coef": 0.3, "every": 64}}
+    diff = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.25, "scale": 64 ** -0.5,
+            "q_temp": {"coef": 0.2, "every": 128}}
     latent = {"heads": heads, "dim": 64, "vdim": 128, "kv_rank": rank, "scale": 64 ** -0.5, "mask": {"size": window}}
     forget = {"heads": heads, "dim": 128, "vdim": 128}
     kinds = [("attention", diff), ("latent_attention", latent), ("hgrn2", forget)]
     ff = {"kind": "dense", "ff": ffn * 3 // 2 // 64 * 64}
     return dict(architecture="Biruvik", vocab=vocab, width=width, norm={"eps": 1e-6}, embedding={"scale": 1.0},
-                logit_softcap=30.0, max_context=8192,
+                logit_softcap=50.0, max_context=8192,
                 layers=[{"type": kinds[i % 3][0], "mixer": dict(kinds[i % 3][1]), "mlp": dict(ff)} for i in range(layers)])
 
 

@@ -80,8 +80,8 @@ B3 = dict(architecture="Biruvik", vocab=53, width=40, norm={"eps": 1e-6}, embedd
 ])
 # sizes of the fast paths: attention on the tensor cores (a window that ends at a tile of keys and one that does not),
 # the recurrence with a head's columns split over CTAs
-B4 = dict(architecture="Biruvik", vocab=90, width=96, norm={"eps": 1e-5}, embedding={"scale": 0.5}, logit_softcap=30.0, layers=[
-    {"type": "attention", "mixer": _diff(4, 1, 32, 32, temp=(0.3, 16)), "mlp": _ff(128)},
+B4 = dict(architecture="Biruvik", vocab=90, width=96, norm={"eps": 2e-6}, embedding={"scale": 0.8}, logit_softcap=20.0, layers=[
+    {"type": "attention", "mixer": _diff(4, 1, 32, 32, temp=(0.35, 16)), "mlp": _ff(128)},
     {"type": "latent_attention", "mixer": _latent(8, 32, 16, 48, window=64), "mlp": None},
     {"type": "hgrn2", "mixer": _hgrn(2, 64, 64), "mlp": _ff(128)},
     {"type": "latent_attention", "mixer": _latent(2, 16, 32, 96, window=37), "mlp": _ff(64)},
@@ -806,11 +806,11 @@ def random_configuration(seed):
         if kind == "attention":
             kv = pick([1, 2, 3])
             mixer = _diff(kv * pick([1, 2, 4]), kv, pick([8, 16, 24, 32, 64]), pick([8, 16, 32, 48, 64, 96]),
-                          diff=pick([0.1, 0.3, 0.5, 0.8]), temp=pick([None, (0.3, 64), (0.1, 1), (1.0, 17)]),
+                          diff=pick([0.1, 0.3, 0.5, 0.8]), temp=pick([None, (0.25, 48), (0.1, 1), (1.0, 17)]),
                           scale=pick([None, 0.2]))
         elif kind == "latent_attention":
             mixer = _latent(pick([1, 2, 4, 5, 8]), pick([8, 16, 32, 48]), pick([8, 16, 24, 64]), pick([12, 16, 32, 48, 80, 96, 160]),
-                            window=pick([1, 3, 16, 50, 64, 136, 200, 1000]), scale=pick([None, 0.2]))
+                            window=pick([1, 3, 16, 50, 64, 130, 200, 1000]), scale=pick([None, 0.2]))
         else:
             mixer = _hgrn(pick([1, 2, 3, 4]), pick([8, 16, 32, 64, 128]), pick([8, 16, 32, 64, 96]))
         mlp = _ff(pick([24, 32, 64, 100, 256])) if rng.random() < 0.75 else None
@@ -820,7 +820,7 @@ def random_configuration(seed):
     if rng.random() < 0.7:
         cfg["embedding"] = {"scale": pick([0.5, 1.0, 2.0, 8.0])}
     if rng.random() < 0.7:
-        cfg["logit_softcap"] = pick([5.0, 30.0, 50.0])
+        cfg["logit_softcap"] = pick([5.0, 25.0, 50.0])
     return cfg, pick([8, 16, 16, 32])
 
 
