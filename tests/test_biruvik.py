@@ -547,9 +547,9 @@ def test_forget_gate_recurrence_in_portions_and_far_memory(dtype, H, kd, vd):
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,dim,vd,page,window,temp", [(4, 2, 16, 24, 16, None, (0.4, 5)), (2, 2, 8, 40, 4, 13, (1.5, 7)),
-                                                         (3, 1, 10, 6, 12, None, (0.2, 3)), (4, 1, 32, 64, 16, None, (0.3, 64)),
+                                                         (3, 1, 10, 6, 12, None, (0.2, 3)), (4, 1, 32, 48, 16, None, (0.35, 48)),
                                                          (1, 1, 16, 16, 8, None, None), (6, 2, 16, 64, 16, 70, (0.5, 1)),
-                                                         (2, 1, 64, 32, 32, None, (0.3, 100))])
+                                                         (2, 1, 64, 32, 32, None, (0.25, 100))])
 def test_differential_attention_and_a_key_far_back(dtype, H, G, dim, vd, page, window, temp):
     """Bias, norm per head and map, query temperature and the cache rows; two maps over the same values; their
     combination.  In portions and single rows over scattered pages.  Map 1 of head 0 of some rows near the end asks

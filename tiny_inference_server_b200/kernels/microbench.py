@@ -501,7 +501,7 @@ def differential_latent_forget(args):
     nq, nk = H * hd, G * hd
     qkv = [torch.randn(n, nq + 2 * nk, **bf) for _ in range(bufs)]
     bias, qw, kw = torch.zeros(nq + 2 * nk, device=dev), torch.ones(dim, device=dev), torch.ones(dim, device=dev)
-    t_new = _graph_time(lambda i: ops.head_norm_store(qkv[i % bufs], H, G, 2, dim, hd, bias, qw, kw, 1e-6, 0.3, 64, q2, plane[:, 0],
+    t_new = _graph_time(lambda i: ops.head_norm_store(qkv[i % bufs], H, G, 2, dim, hd, bias, qw, kw, 1e-6, 0.2, 128, q2, plane[:, 0],
                                                       plane[:, 1], table, pos, slot, page, fault), 12)
     wq, wk = torch.ones(nq, device=dev), torch.ones(nk, device=dev)
     t_like = _graph_time(lambda i: ops.norm_mix_store(qkv[i % bufs], nq, nk, nk, wq, wk, 1e-6, None, None, plane[:, 0], plane[:, 1],
