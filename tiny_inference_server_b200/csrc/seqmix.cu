@@ -463,6 +463,82 @@ head_norm_store_kernel(const T* __restrict__ qkv, int ld, int H, int G, int M, i
     }
 }
 
+// The same with 16-byte vectors, for runs, value rows and strides that are multiples of a vector and runs of
+// `lanes` = dim / vector lanes, a power of two up to 32: `lanes` neighbouring lanes hold a run in registers (one pass
+// over the input), 256 / lanes runs at a time.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_store_vec_kernel(const T* __restrict__ qkv, int ld, int H, int G, int M, int dim, int vdim,
+                           const float* __restrict__ bias, const float* __restrict__ wq, const float* __restrict__ wk,
+                           float eps, float temp_coef, int temp_every, T* __restrict__ q_out, int ldq,
+                           T* __restrict__ k_pages, size_t k_page_stride, size_t k_head_stride, T* __restrict__ v_pages,
+                           size_t v_page_stride, size_t v_head_stride, int page_size, int num_pages,
+                           const int* __restrict__ block_table, int bt_stride, const int* __restrict__ positions,
+                           const int* __restrict__ row_slot, int* __restrict__ fault) {
+    constexpr int N = Vec16<T>::N;
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+    if (pos < 0 || page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicExch(fault, 7);
+        return;
+    }
+    const float temp = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
+    const int in_page = pos % page_size;
+    const int q_runs = H * M, k_runs = G * M, kw = M * dim, runs = q_runs + k_runs;
+    const int lanes = dim / N, groups = blockDim.x / lanes;
+    const int group = threadIdx.x / lanes, e0 = (threadIdx.x % lanes) * N;
+    pdl_wait();
+    const T* row = qkv + (size_t)r * ld;
+    float x[N], zero[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) zero[e] = 0.f;
+    for (int base = 0; base < runs; base += groups) {       // every lane of a warp stays in the loop for the shuffles
+        const int run = base + group;
+        const bool live = run < runs;
+        const bool is_q = run < q_runs;
+        const int at = run * dim + e0;
+        float ss = 0.f;
+        if (live) {
+            Vec16<T>::load(row + at, x);
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                if (bias != nullptr) x[e] += bias[at + e];
+                ss = fmaf(x[e], x[e], ss);
+            }
+        }
+        for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!live) continue;
+        const float* w = is_q ? wq : wk;
+        float f = w != nullptr ? rsqrtf(ss / (float)dim + eps) : 1.f;
+        if (is_q) f *= temp;
+#pragma unroll
+        for (int e = 0; e < N; ++e) x[e] = x[e] * f * (w != nullptr ? w[e0 + e] : 1.f);
+        const int m = run % M;
+        if (is_q) {
+            T* dst = q_out + (size_t)r * ldq + (size_t)run * kw + e0;
+            for (int mm = 0; mm < M; ++mm) Vec16<T>::store(dst + mm * dim, mm == m ? x : zero);
+        } else {
+            const int kvh = (run - q_runs) / M;
+            Vec16<T>::store(k_pages + (size_t)page * k_page_stride + (size_t)kvh * k_head_stride + (size_t)in_page * kw +
+                            m * dim + e0, x);
+        }
+    }
+    const int v_at = runs * dim;
+    for (int i = threadIdx.x * N; i < G * vdim; i += blockDim.x * N) {
+        const int kvh = i / vdim, e = i - kvh * vdim;
+        Vec16<T>::load(row + v_at + i, x);
+        if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) x[j] += bias[v_at + i + j];
+        }
+        Vec16<T>::store(v_pages + (size_t)page * v_page_stride + (size_t)kvh * v_head_stride + (size_t)in_page * vdim + e, x);
+    }
+}
+
 TIS_API int tis_head_norm_store(int dtype, const void* qkv, int ld, int H, int G, int M, int dim, int vdim,
                                 const float* bias, const float* wq, const float* wk, float eps, float temp_coef,
                                 int temp_every, void* q_out, int ldq, void* k_pages, size_t k_page_stride,
@@ -475,6 +551,18 @@ TIS_API int tis_head_norm_store(int dtype, const void* qkv, int ld, int H, int G
         tis_set_error("head_norm_store: %d query heads, %d kv heads, %d maps of %d elements, value width %d, page size %d, "
                       "row lengths %d in and %d out", H, G, M, dim, vdim, page_size, ld, ldq);
         return TIS_BAD_SIZE;
+    }
+    const int per = dtype == TIS_BF16 ? 8 : 4;
+    const int lanes = dim / per;
+    if (dim % per == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0 && vdim % per == 0 && ld % per == 0 && ldq % per == 0 &&
+        k_page_stride % per == 0 && k_head_stride % per == 0 && v_page_stride % per == 0 && v_head_stride % per == 0 &&
+        ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
+        TIS_DISPATCH_DTYPE(dtype, T,
+            tis_launch(head_norm_store_vec_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)qkv, ld, H, G, M, dim, vdim,
+                       bias, wq, wk, eps, temp_coef, temp_every, (T*)q_out, ldq, (T*)k_pages, k_page_stride, k_head_stride,
+                       (T*)v_pages, v_page_stride, v_head_stride, page_size, num_pages, block_table, bt_stride, positions,
+                       row_slot, fault));
+        return tis_check_launch("head_norm_store");
     }
     TIS_DISPATCH_DTYPE(dtype, T,
         tis_launch(head_norm_store_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)qkv, ld, H, G, M, dim, vdim, bias,

@@ -506,7 +506,7 @@ def differential_latent_forget(args):
     wq, wk = torch.ones(nq, device=dev), torch.ones(nk, device=dev)
     t_like = _graph_time(lambda i: ops.norm_mix_store(qkv[i % bufs], nq, nk, nk, wq, wk, 1e-6, None, None, plane[:, 0], plane[:, 1],
                                                       table, pos, slot, page, fault), 12)
-    put(f"bias, norms, temperature, cache write, {n} rows", t_new, n * ((nq + 2 * nk) * 2 + 2 * nq + 2 * nk) * 2, "GB/s", t_like,
+    put(f"bias, norms, temperature, cache write, {n} rows", t_new, n * ((nq + 2 * nk) + 2 * nq + 2 * nk) * 2, "GB/s", t_like,
         n * (nq + 2 * nk) * 2 * 2)
     mp = [torch.randn(n, 2 * H * hd, **bf) for _ in range(bufs)]
     t_new = _graph_time(lambda i: ops.diff_combine(mp[i % bufs], 0.8, 1e-6, 0.7, ol, H, hd, slot), 12)
