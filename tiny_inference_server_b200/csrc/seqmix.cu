@@ -794,7 +794,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                   const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps, float unit_eps,
                   float q_scale, float* __restrict__ state, size_t state_stride, T* __restrict__ out, int ldo,
                   const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int k_dim_rt,
-                  int v_dim, int decay_mode, int gate_act, float* __restrict__ o_raw) {
+                  int v_dim, int decay_mode, int gate_act, float* __restrict__ o_raw, int state_in_place) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     const int head = blockIdx.x, r0 = blockIdx.y;
@@ -817,6 +817,9 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     const bool corrects = !plain && !forget;            // the delta rule proper: the state is corrected towards v
     const float decay_rate = plain ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * k_dim * v_dim;
+    // a state too large for shared memory is walked where it lies (DIM == 0 only): a thread touches its own column alone
+    const bool in_place = DIM == 0 && state_in_place != 0;
+    if (in_place) S_sh = S_glob;
     constexpr int REG = DIM > 0 ? DIM : 1;
     float S[REG];
     pdl_wait();
@@ -824,7 +827,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
         if (DIM > 0) {
 #pragma unroll
             for (int i = 0; i < REG; ++i) S[i] = S_glob[(size_t)i * v_dim + tid];
-        } else {
+        } else if (!in_place) {
             for (int i = 0; i < k_dim; ++i) S_sh[i * v_dim + tid] = S_glob[(size_t)i * v_dim + tid];
         }
     }
@@ -940,7 +943,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
         if (DIM > 0) {
 #pragma unroll
             for (int i = 0; i < REG; ++i) S_glob[(size_t)i * v_dim + tid] = S[i];
-        } else {
+        } else if (!in_place) {
             for (int i = 0; i < k_dim; ++i) S_glob[(size_t)i * v_dim + tid] = S_sh[i * v_dim + tid];
         }
     }
@@ -1232,7 +1235,12 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
     int threads = (v_dim + 31) / 32 * 32;
     if (threads < 128) threads = 128;                  // warps to prepare and normalise a chunk with
     size_t smem = sizeof(float) * ((size_t)DELTA_CHUNK * (3 * k_dim + 2 * v_dim + 1) + (DIM > 0 ? 0 : (size_t)k_dim * v_dim));
-    if (smem > 200 * 1024) {
+    int in_place = 0;
+    if (smem > 200 * 1024) {                           // the state stays in global memory
+        in_place = 1;
+        smem = sizeof(float) * ((size_t)DELTA_CHUNK * (3 * k_dim + 2 * v_dim + 1));
+    }
+    if (smem > 200 * 1024 || (in_place && DIM > 0)) {
         tis_set_error("delta_rule: key width %d x value width %d does not fit shared memory", k_dim, v_dim);
         return TIS_BAD_SIZE;
     }
@@ -1240,7 +1248,7 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
         cudaFuncSetAttribute(delta_rule_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     tis_launch(delta_rule_kernel<T, DIM>, dim3(H, n), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
                A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, out, ldo, row_slot, row_last, H, G,
-               k_dim, v_dim, decay_mode, gate_act, decay_mode == DECAY_CONSTANT ? o_raw : (float*)nullptr);
+               k_dim, v_dim, decay_mode, gate_act, decay_mode == DECAY_CONSTANT ? o_raw : (float*)nullptr, in_place);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK || decay_mode != DECAY_CONSTANT) return st;
     tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(256), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
