@@ -477,7 +477,7 @@ def _portions(L, cuts, alone=4):
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,kd,vd", [(2, 16, 24), (1, 16, 16), (3, 10, 6), (2, 64, 64), (1, 128, 32), (4, 32, 96), (2, 32, 128),
-                                      (1, 256, 256), (2, 160, 224)])
+                                      (1, 256, 256), (2, 160, 224), (2, 16, 320), (1, 40, 520)])
 def test_forget_gate_recurrence_in_portions_and_far_memory(dtype, H, kd, vd):
     """Two sequences side by side in slots 2 and 0, in portions of 1..70 rows, equal the plain recurrence over the
     whole sequences.  Head 0's gate is shut (f = 1: nothing forgotten, nothing written) but for position 1, where it

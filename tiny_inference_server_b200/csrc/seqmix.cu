@@ -768,9 +768,9 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
 // One CTA per (head, row); the CTAs of rows that are not the first of their request in the step leave at once (rows
 // are the slowest grid dimension, so that the CTAs with work are not queued behind thousands of those).
 // Every column of S is a recurrence of its own: a thread keeps one column (in registers when DIM > 0 is the key
-// width, else in shared memory).  Tokens are taken CHUNK at a time: all threads prepare q^, k^, g, beta and v of
-// the chunk, then every thread walks its column through the chunk without a barrier, then the outputs of the
-// chunk are normalised, a warp a token.
+// width, else in shared memory, or in place in global memory where it does not fit there; up to 1024 columns).
+// Tokens are taken CHUNK at a time: all threads prepare q^, k^, g, beta and v of the chunk, then every thread walks
+// its column through the chunk without a barrier, then the outputs of the chunk are normalised, a warp a token.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int DELTA_CHUNK = 16;
 
@@ -788,7 +788,7 @@ __device__ __forceinline__ float gate_f(float x, int act) { const float s = 1.f 
 enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2, DECAY_FORGET_GATE = 3 };
 
 template <typename T, int DIM>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(DIM > 0 ? 256 : 1024)
 delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
                   int lda, const T* __restrict__ gate, int ldg, const float* __restrict__ A_log,
                   const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps, float unit_eps,
@@ -1307,8 +1307,8 @@ static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const voi
         TIS_DELTA_SPLIT(128, 32, 4, 32)
 #undef TIS_DELTA_SPLIT
     }
-    if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 256) {
-        tis_set_error("delta_rule: %d heads, %d query/key heads, key width %d, value width %d (at most 256)", H, G, k_dim,
+    if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 1024) {
+        tis_set_error("delta_rule: %d heads, %d query/key heads, key width %d, value width %d (at most 1024)", H, G, k_dim,
                       v_dim);
         return TIS_BAD_SIZE;
     }
@@ -1319,7 +1319,7 @@ static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const voi
             state_stride, (T*)out, ldo, row_slot, row_last, n, H, G, k_dim, v_dim, decay_mode, gate_act, o_raw,        \
             stream));                                                                                                 \
         break;
-    switch (k_dim) {
+    switch (v_dim <= 256 ? k_dim : 0) {                 // a column's state in registers: CTAs of up to 256 columns
         TIS_DELTA_CASE(16)
         TIS_DELTA_CASE(32)
         TIS_DELTA_CASE(64)
