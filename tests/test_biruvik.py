@@ -752,6 +752,27 @@ def test_norm_behind_a_sublayer_activations_and_soft_cap(dtype, n, d):
     _close(rows, table.double()[toks] * 0.7, 1e-6, "scaled embedding")
 
 
+@gpu
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("n,K,N", [(1, 256, 512), (8, 1536, 6144), (33, 512, 1096), (8, 3072, 12288), (200, 256, 512)])
+def test_product_with_the_activation_in_its_epilogue(kind, n, K, N):
+    """``act(a @ w)``: few rows take a weight-streaming product whose epilogue applies the activation to the 32-bit sums
+    (no activation kernel is launched), many rows the product and then the activation kernel."""
+    from tiny_inference_server_b200.kernels import ops
+    torch.manual_seed(n + K)
+    a = (torch.randn(n, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(K, N) / math.sqrt(K)).to(torch.bfloat16)
+    before = dict(ops.calls)
+    got = ops.gemm_act(a.cuda(), w.cuda(), kind)
+    torch.cuda.synchronize()
+    fused = sum(ops.calls[k] - before.get(k, 0) for k in ("gemm_skinny", "gemm_stream"))
+    if (n, K) == (8, 1536):                              # a decode step's rows at a small model's sizes
+        assert fused == 1, dict(ops.calls)
+    if n > 64:
+        assert fused == 0, dict(ops.calls)
+    _close(got, plain.ACTIVATIONS[kind](a.double() @ w.double()), 1e-2, f"{kind} behind a product of {n} rows")
+
+
 # ------------------------------------------------------------------------------------------------
 # GPU: the whole model through the engine
 # ------------------------------------------------------------------------------------------------

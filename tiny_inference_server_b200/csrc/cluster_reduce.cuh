@@ -18,7 +18,16 @@ namespace cluster_reduce {
 
 constexpr int STRIP = 64;             // columns of a strip
 constexpr int CONSUMERS = 128;        // threads that hold accumulators: four warps, 16 columns each
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2 };
+// EPI_RELU2 .. EPI_SILU: a store through an activation (the square of relu; gelu in its tanh form; silu), applied to the
+// 32-bit sum
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2, EPI_RELU2 = 3, EPI_GELU_TANH = 4, EPI_SILU = 5 };
+
+__device__ __forceinline__ float epilogue_act(float x, int epi) {
+    if (epi == EPI_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (epi == EPI_GELU_TANH) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    if (epi == EPI_SILU) return x / (1.f + expf(-x));
+    return x;
+}
 
 struct Epilogue {
     bf16* out; int ldo;
@@ -204,8 +213,9 @@ __device__ __forceinline__ void push_reduce_store(const float (&acc)[MT][2][4], 
             for (unsigned r = 0; r < ksplit; ++r) sum += recv[(r * rpr + li) * STRIP + col];
             if (scaled) sum *= row_factor[row];
         }
-        if (e.epi == EPI_STORE) {
-            if (valid && strip * STRIP + col < e.N) e.out[(size_t)row * e.ldo + strip * STRIP + col] = __float2bfloat16_rn(sum);
+        if (e.epi != EPI_SWIGLU) {                      // a plain store, or one through an activation
+            if (valid && strip * STRIP + col < e.N)
+                e.out[(size_t)row * e.ldo + strip * STRIP + col] = __float2bfloat16_rn(epilogue_act(sum, e.epi));
         } else {
             // the strip is [32 gate | 32 up]: out column strip*32 + j = silu(gate_j) * up_j
             pair[half][col] = sum;

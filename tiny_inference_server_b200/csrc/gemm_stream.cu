@@ -24,6 +24,8 @@ using namespace tc;
 using cluster_reduce::EPI_STORE;
 using cluster_reduce::EPI_SWIGLU;
 using cluster_reduce::EPI_RESIDUAL;
+using cluster_reduce::EPI_RELU2;
+using cluster_reduce::EPI_SILU;
 
 constexpr int BN = 64;            // columns of a strip
 constexpr int BK = 64;            // rows of K per box
@@ -233,7 +235,7 @@ TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw
         tis_set_error("gemm_stream: ksplit %d must be 1, 2, 4 or 8", ksplit);
         return TIS_BAD_SIZE;
     }
-    if (epi < EPI_STORE || epi > EPI_RESIDUAL) {
+    if (epi < EPI_STORE || epi > EPI_SILU) {
         tis_set_error("gemm_stream: unknown epilogue %d", epi);
         return TIS_BAD_SIZE;
     }

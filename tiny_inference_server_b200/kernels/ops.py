@@ -115,6 +115,8 @@ SKINNY_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SKINNY_SWIGLU_MAX_ROWS", "16"))
 #: TIS_SWAP_SWIGLU_MAX_ROWS overrides (0: never).
 SWAP_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SWAP_SWIGLU_MAX_ROWS", "32"))
 EPI_STORE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
+#: a store through an activation, by the activation's name (the weight-streaming products)
+EPI_ACT = {"relu2": 3, "gelu_tanh": 4, "silu": 5}
 #: the norm between two weight-streaming products is folded into them (``ResidualSink`` / ``ScaledRows``);
 #: TIS_FUSED_NORM=0 keeps the norm kernel
 FUSED_NORM = os.environ.get("TIS_FUSED_NORM", "1") != "0"
@@ -303,10 +305,11 @@ def _sink_fits(sink: Optional[ResidualSink], n: int, cols: int, out) -> bool:
 
 
 def gemm_stream(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
-                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None):
+                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None, act: Optional[str] = None):
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by the TMA-fed weight-streaming kernel; with ``swiglu``
     the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2).  ``a`` may be ``ScaledRows``;
-    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``."""
+    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``; with ``act`` (a key of
+    ``EPI_ACT``; not with ``swiglu`` or ``sink``) the 32-bit sums pass that activation on their way out."""
     lib = library()
     scaled = a if isinstance(a, ScaledRows) else None
     if scaled is not None:
@@ -321,21 +324,30 @@ def gemm_stream(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: 
     elif out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
     calls["gemm_stream"] += 1
-    epi = EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+    epi = _epilogue(sink, swiglu, act)
     _check(lib.tis_gemm_stream_fused(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
                                      ksplit or _ksplit(cols, k), epi, *head, *tail, _p(tc_fault()), _stream()), lib)
     return result if sink is not None else out
 
 
+def _epilogue(sink, swiglu: bool, act: Optional[str]) -> int:
+    if act is not None:
+        if sink is not None or swiglu or act not in EPI_ACT:
+            raise KernelError(f"activation epilogue {act!r}: known are {sorted(EPI_ACT)}, and not with gating or a sink")
+        return EPI_ACT[act]
+    return EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+
+
 def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
-                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None):
+                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None, act: Optional[str] = None):
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by a weight-streaming kernel; with ``swiglu``
     the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2).  ``a`` may be ``ScaledRows``;
-    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``."""
+    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``; ``act`` as in
+    ``gemm_stream``."""
     rows = a.rows if isinstance(a, ScaledRows) else a
     if (_stream_pays(rows.shape[0], rows.shape[1], w.shape[1], ksplit) and rows.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and _stream_fits(rows.shape[0], rows.shape[1], ksplit or _ksplit(w.shape[1], rows.shape[1]))):
-        return gemm_stream(a, w, out, swiglu, ksplit, sink)
+        return gemm_stream(a, w, out, swiglu, ksplit, sink, act)
     lib = library()
     scaled = a if isinstance(a, ScaledRows) else None
     a = rows
@@ -349,7 +361,7 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: 
     elif out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
     calls["gemm_skinny"] += 1
-    epi = EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+    epi = _epilogue(sink, swiglu, act)
     _check(lib.tis_gemm_skinny_fused(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
                                      ksplit or _ksplit(cols, k), epi, *head, *tail, _p(tc_fault()), _stream()), lib)
     return result if sink is not None else out
@@ -441,14 +453,27 @@ def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
     return out
 
 
-def gemm(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, sink: Optional[ResidualSink] = None):
+def gemm(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, sink: Optional[ResidualSink] = None,
+         act: Optional[str] = None):
     """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Few bfloat16
     rows go to the weight-streaming kernel of this library, many to its tcgen05 kernel,
     everything else to the library product.
 
     ``a`` may be ``ScaledRows``.  With ``sink``, a product that goes to a weight-streaming kernel adds its
     result to the residual stream itself and returns ``ScaledRows`` for the norm that follows; any other
-    product ignores the sink and returns its result, which the caller adds as before."""
+    product ignores the sink and returns its result, which the caller adds as before.  With ``act`` (not with a
+    sink) the result passes that activation: in the epilogue of a weight-streaming kernel, else by the activation
+    kernel behind the product."""
+    if act is not None:
+        if sink is not None:
+            raise KernelError("gemm: an activation and a sink do not go together")
+        rows = a.rows if isinstance(a, ScaledRows) else a
+        streams = _stream_pays(rows.shape[0], rows.shape[1], w.shape[1]) and rows.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+        if (_skinny_ok(rows, w) and (streams or _ring_tiles(w.shape[1], rows.shape[1]) <= RING_MAX_TILES)) or \
+                (_skinny_ok(rows, w, STREAM_MAX_ROWS) and streams):
+            return gemm_skinny(a, w, out, act=act)
+        h = gemm(a, w, out)
+        return activation(h, h, act)
     scaled = a if isinstance(a, ScaledRows) else None
     if scaled is not None:
         a = scaled.rows
@@ -818,9 +843,9 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
 
 
 def gemm_act(a, w: torch.Tensor, kind: str) -> torch.Tensor:
-    """``act(a @ w)``: the product, then the activation kernel.  ``a`` may be ``ScaledRows``."""
-    h = gemm(a, w)
-    return activation(h, h, kind)
+    """``act(a @ w)``: few bfloat16 rows: a weight-streaming product with the activation in its epilogue; else the
+    product, then the activation kernel.  ``a`` may be ``ScaledRows``."""
+    return gemm(a, w, act=kind)
 
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
