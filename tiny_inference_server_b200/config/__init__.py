@@ -1,5 +1,5 @@
-from .model_config import ConfigError, GqaMtpConfig, KefisunConfig, MizidraConfig, BiruvikConfig, read_config_json, write_config_json, UPSTREAM_ALIASES
+from .model_config import ConfigError, GqaMtpConfig, KefisunConfig, MizidraConfig, BiruvikConfig, KubolornConfig, read_config_json, write_config_json, UPSTREAM_ALIASES
 from .engine_config import EngineConfig
 
-__all__ = ["ConfigError", "GqaMtpConfig", "KefisunConfig", "MizidraConfig", "BiruvikConfig", "EngineConfig", "read_config_json", "write_config_json",
+__all__ = ["ConfigError", "GqaMtpConfig", "KefisunConfig", "MizidraConfig", "BiruvikConfig", "KubolornConfig", "EngineConfig", "read_config_json", "write_config_json",
            "UPSTREAM_ALIASES"]

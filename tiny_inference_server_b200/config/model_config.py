@@ -606,3 +606,211 @@ class BiruvikConfig:
         if self.eos_token_id is not None:
             d["eos_token_id"] = self.eos_token_id
         return d
+
+
+@dataclass
+class KubolornConfig:
+    """Configuration of the Kubolorn decoder: a scaled embedding with a second table addressed by a hash of the token and
+    its predecessor, under a norm of its own; layers whose two sublayers read the same stream, ``x += mixer(norm1(x)) +
+    ff(norm2(x))``, each behind a short causal convolution of its input; RMS norms in groups; a span of layers that runs
+    several times in a row with the same weights; logits from the embedding matrix.
+
+    ``config.json`` is nested: ``vocab``, ``width``, ``norm`` = ``eps, groups``, ``embedding`` = ``scale`` and ``bigram`` =
+    ``buckets, mul_prev, mul_cur``, ``canon.taps``, ``loop`` = ``start, stop, times`` (layers start..stop-1 run ``times``
+    times), and ``layers``, a list with, per layer, ``type``, ``mixer`` (the sizes and constants of that kind of mixer) and
+    ``mlp`` (null: none).  The kinds:
+
+    * ``gla`` — ``heads, dim, vdim, tau``: linear attention with a gate per head and key channel; the rank of the gate's
+      low-rank projection is the first dimension of the tensor ``l<i>.mix.a1`` (``complete_from_shapes``);
+    * ``parallel`` — ``left`` = ``heads, kv_heads, dim, vdim, scale, rot`` (``base, dims`` and, optionally, ``scaling`` =
+      ``factor, original, fast, slow``), ``right`` = ``heads, vdim, state, groups, norm_groups, conv``, ``left_scale,
+      right_scale``: attention whose values are its keys before rotation beside a selective state space.
+
+    ``mlp``: ``kind`` ``dense`` with ``ff``, or ``moe`` with ``expert.ff`` and ``router`` = ``experts, top``.  The design
+    has no context limit of its own: ``max_context`` (optional) bounds what the engine lays out (block tables, rotation
+    tables)."""
+
+    architecture: ClassVar[str] = "Kubolorn"
+    MIXERS: ClassVar[tuple] = ("gla", "parallel")
+
+    vocab_size: int
+    hidden_size: int
+    layers: list
+    rms_norm_eps: float = 1e-6
+    norm_groups: int = 1
+    embedding_scale: float = 1.0
+    bigram: Optional[dict] = None               # buckets, mul_prev, mul_cur
+    canon_taps: Optional[int] = None
+    loop: Optional[dict] = None                 # start, stop, times
+    max_context: int = 1 << 16
+    eos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        errs = []
+        num = (int, float)
+        for name in ("vocab_size", "hidden_size", "norm_groups", "max_context"):
+            if not _positive_int(getattr(self, name)):
+                errs.append(f"{name} must be a positive integer, got {getattr(self, name)!r}")
+        if not isinstance(self.layers, list) or not self.layers:
+            errs.append("layers must be a non-empty list")
+        if errs:
+            raise ConfigError("; ".join(errs))
+        if self.hidden_size % self.norm_groups:
+            errs.append(f"norm.groups {self.norm_groups} does not divide the width {self.hidden_size}")
+        if not (self.rms_norm_eps >= 0):
+            errs.append(f"norm.eps must be >= 0, got {self.rms_norm_eps}")
+        if self.canon_taps is not None and not (_positive_int(self.canon_taps) and self.canon_taps <= 16):
+            errs.append(f"canon.taps must be 1..16, got {self.canon_taps!r}")
+        if self.bigram is not None:
+            bad = [k for k in ("buckets", "mul_prev", "mul_cur") if not isinstance(self.bigram.get(k), int)]
+            if bad or self.bigram["buckets"] <= 0 or self.bigram["mul_prev"] < 0 or self.bigram["mul_cur"] < 0:
+                errs.append("embedding.bigram needs a positive integer buckets and integers mul_prev, mul_cur >= 0")
+        if self.loop is not None:
+            lp = self.loop
+            if not all(isinstance(lp.get(k), int) and not isinstance(lp.get(k), bool) for k in ("start", "stop", "times")) \
+                    or not (0 <= lp["start"] <= lp["stop"] <= len(self.layers)) or lp["times"] < 1:
+                errs.append(f"loop needs 0 <= start <= stop <= {len(self.layers)} and times >= 1, got {lp!r}")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, dict) else None
+            if kind not in self.MIXERS:
+                errs.append(f"layers[{i}].type must be one of {self.MIXERS}, got {kind!r}")
+                continue
+            m = layer.get("mixer")
+            if not isinstance(m, dict):
+                errs.append(f"layers[{i}].mixer is missing")
+                continue
+            if kind == "gla":
+                bad = [k for k in ("heads", "dim", "vdim") if not _positive_int(m.get(k))]
+                if bad:
+                    errs.append(f"layers[{i}].mixer: {', '.join(bad)} must be positive integers")
+                if not isinstance(m.get("tau"), num) or isinstance(m.get("tau"), bool) or not m["tau"] > 0:
+                    errs.append(f"layers[{i}].mixer.tau must be a positive number")
+            else:
+                left, right = m.get("left"), m.get("right")
+                if not isinstance(left, dict) or not isinstance(right, dict):
+                    errs.append(f"layers[{i}].mixer needs left and right")
+                    continue
+                bad = [k for k in ("heads", "kv_heads", "dim") if not _positive_int(left.get(k))]
+                if bad:
+                    errs.append(f"layers[{i}].mixer.left: {', '.join(bad)} must be positive integers")
+                else:
+                    if left["heads"] % left["kv_heads"]:
+                        errs.append(f"layers[{i}].mixer.left: {left['heads']} heads are not a multiple of "
+                                    f"{left['kv_heads']} kv heads")
+                    if left.get("vdim", left["dim"]) != left["dim"]:
+                        errs.append(f"layers[{i}].mixer.left: the values are the keys, so vdim must equal dim")
+                    rot = left.get("rot")
+                    if rot is not None:
+                        dims = rot.get("dims", left["dim"]) if isinstance(rot, dict) else None
+                        if not isinstance(rot, dict) or not isinstance(rot.get("base"), num) or not rot["base"] > 0:
+                            errs.append(f"layers[{i}].mixer.left.rot.base is missing")
+                        elif not _positive_int(dims) or dims % 2 or dims > left["dim"]:
+                            errs.append(f"layers[{i}].mixer.left: rot.dims must be even and at most dim ({left['dim']})")
+                        elif rot.get("scaling"):
+                            sc = rot["scaling"]
+                            miss = [k for k in ("factor", "original", "fast", "slow") if not isinstance(sc.get(k), num)]
+                            if miss:
+                                errs.append(f"layers[{i}].mixer.left.rot.scaling lacks {', '.join(miss)}")
+                if not isinstance(left.get("scale"), num) or isinstance(left.get("scale"), bool):
+                    errs.append(f"layers[{i}].mixer.left.scale is missing")
+                bad = [k for k in ("heads", "vdim", "state", "groups", "conv") if not _positive_int(right.get(k))]
+                if bad:
+                    errs.append(f"layers[{i}].mixer.right: {', '.join(bad)} must be positive integers")
+                else:
+                    if right["heads"] % right["groups"]:
+                        errs.append(f"layers[{i}].mixer.right: {right['heads']} heads are not a multiple of "
+                                    f"{right['groups']} groups")
+                    ng = right.get("norm_groups", 1)
+                    if not _positive_int(ng) or (right["heads"] * right["vdim"]) % ng:
+                        errs.append(f"layers[{i}].mixer.right.norm_groups must divide heads * vdim")
+                    if right["conv"] > 16:
+                        errs.append(f"layers[{i}].mixer.right.conv must be 1..16, got {right['conv']}")
+                for k in ("left_scale", "right_scale"):
+                    if not isinstance(m.get(k, 1.0), num) or isinstance(m.get(k, 1.0), bool):
+                        errs.append(f"layers[{i}].mixer.{k} must be a number")
+            f = layer.get("mlp")
+            if f is None:
+                continue
+            if not isinstance(f, dict) or f.get("kind") not in ("dense", "moe"):
+                errs.append(f"layers[{i}].mlp.kind must be 'dense' or 'moe', got {f.get('kind') if isinstance(f, dict) else f!r}")
+            elif f["kind"] == "dense":
+                if not _positive_int(f.get("ff")):
+                    errs.append(f"layers[{i}].mlp.ff must be a positive integer")
+            else:
+                r = f.get("router")
+                if not isinstance(f.get("expert"), dict) or not _positive_int(f["expert"].get("ff")):
+                    errs.append(f"layers[{i}].mlp.expert.ff must be a positive integer")
+                if not isinstance(r, dict) or not _positive_int(r.get("experts")) or not _positive_int(r.get("top")):
+                    errs.append(f"layers[{i}].mlp.router needs experts and top")
+                elif r["top"] > r["experts"]:
+                    errs.append(f"layers[{i}].mlp.router.top {r['top']} exceeds the {r['experts']} experts")
+        if self.torch_dtype not in ("bfloat16", "float32"):
+            errs.append(f"torch_dtype must be bfloat16 or float32, got {self.torch_dtype!r}")
+        if errs:
+            raise ConfigError("; ".join(errs))
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    def layer_runs(self) -> list:
+        """The layers in running order: the looped span several times in a row."""
+        n = len(self.layers)
+        if not self.loop:
+            return list(range(n))
+        a, b, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+        return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
+
+    def complete_from_shapes(self, shapes: dict) -> None:
+        """The rank of a ``gla`` mixer's low-rank gate projection is not in config.json: it is the first dimension of the
+        layer's ``mix.a1``."""
+        for i, layer in enumerate(self.layers):
+            if layer["type"] == "gla" and "decay_rank" not in layer["mixer"]:
+                name = f"l{i}.mix.a1"
+                if name not in shapes or len(shapes[name]) != 2:
+                    raise ConfigError(f"the tensor {name!r} (rank, width) is missing: it gives the rank of layer {i}'s "
+                                      f"gate projection")
+                layer["mixer"]["decay_rank"] = int(shapes[name][0])
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "KubolornConfig":
+        missing = [k for k in ("vocab", "width", "layers") if k not in raw]
+        if missing:
+            raise ConfigError(f"config for architecture {cls.architecture!r}: missing keys: " + ", ".join(missing))
+        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=copy.deepcopy(raw["layers"]))
+        norm = raw.get("norm")
+        if isinstance(norm, dict):
+            if "eps" in norm:
+                d["rms_norm_eps"] = float(norm["eps"])
+            if "groups" in norm:
+                d["norm_groups"] = norm["groups"]
+        emb = raw.get("embedding")
+        if isinstance(emb, dict):
+            if "scale" in emb:
+                d["embedding_scale"] = float(emb["scale"])
+            if emb.get("bigram"):
+                d["bigram"] = dict(emb["bigram"])
+        if isinstance(raw.get("canon"), dict) and raw["canon"].get("taps") is not None:
+            d["canon_taps"] = raw["canon"]["taps"]
+        if raw.get("loop"):
+            d["loop"] = dict(raw["loop"])
+        for k in ("max_context", "eos_token_id", "torch_dtype"):
+            if k in raw:
+                d[k] = raw[k]
+        return cls(**d)
+
+    def to_dict(self) -> dict:
+        emb = {"scale": self.embedding_scale}
+        if self.bigram is not None:
+            emb["bigram"] = dict(self.bigram)
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "embedding": emb,
+             "norm": {"eps": self.rms_norm_eps, "groups": self.norm_groups}, "layers": copy.deepcopy(self.layers),
+             "max_context": self.max_context, "torch_dtype": self.torch_dtype}
+        if self.canon_taps is not None:
+            d["canon"] = {"taps": self.canon_taps}
+        if self.loop is not None:
+            d["loop"] = dict(self.loop)
+        if self.eos_token_id is not None:
+            d["eos_token_id"] = self.eos_token_id
+        return d

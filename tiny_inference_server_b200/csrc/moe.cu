@@ -79,13 +79,14 @@ __device__ __forceinline__ void fill_f32(float* dst, const T* __restrict__ src, 
 // groups > 0 the experts form that many groups of E / groups neighbours, a group's strength is the sum of its two
 // largest picks, and only the experts of the `keep` strongest groups stay in the race;  the `top` largest picks
 // win (the lower index on a tie);  weights: their s over the sum of those (+ weight_eps).  Also sigmoid(w_sg . x)
-// if w_sg is given.
+// if w_sg is given.  score_kind 1: the logits themselves are the picks (correction added if given) and the weights are
+// the softmax over the chosen experts' logits only.
 // ------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(2 * MOE_THREADS)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr, const float* __restrict__ corr,
                  const float* __restrict__ w_sg, int d, int E, int groups, int keep, int top, float weight_eps,
-                 int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate) {
+                 int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate, int score_kind) {
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;                  // [d]
     float* sc = xs + d;                // [E]  sigmoid scores
@@ -107,7 +108,7 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr,
         if (lane == 0) {
             for (int j = 0; j < (e1 != e0 ? 2 : 1); ++j) {
                 const int e = j == 0 ? e0 : e1;
-                const float s = 1.f / (1.f + expf(-z[j]));
+                const float s = (score_kind == 1 && e < E) ? z[j] : 1.f / (1.f + expf(-z[j]));
                 if (e < E) { sc[e] = s; pick[e] = s + (corr != nullptr ? corr[e] : 0.f); }
                 else shared_gate[r] = s;
             }
@@ -149,20 +150,39 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr,
         weights[(size_t)r * top + k] = sc[best];
         total += sc[best];
     }
+    if (score_kind == 1) {                                 // softmax over the chosen logits
+        float big = -INFINITY;
+        for (int k = 0; k < top; ++k) big = fmaxf(big, weights[(size_t)r * top + k]);
+        total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float e = expf(weights[(size_t)r * top + k] - big);
+            weights[(size_t)r * top + k] = e;
+            total += e;
+        }
+        for (int k = 0; k < top; ++k) weights[(size_t)r * top + k] /= total;
+        return;
+    }
     const float inv = 1.f / (total + weight_eps);
     for (int k = 0; k < top; ++k) weights[(size_t)r * top + k] *= inv;
 }
 
 // ------------------------------------------------------------------------------------------------------------
 // hidden[r * top + k][j] = silu(Wg[e][j] . x[r]) * (Wu[e][j] . x[r]),  e = chosen[r][k];  w_gu (E, 2, F, d).
+// act >= 0: units without a gate, hidden = act(Wu[e][j] . x[r]) with w_gu (E, F, d) and act 0 relu^2, 1 gelu (tanh), 2 silu.
 // A CTA per (row and choice, block of COLS hidden columns); a warp a column at a time.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int MOE_COLS = 16;
 
+__device__ __forceinline__ float unit_act(float x, int kind) {
+    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == 1) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.f + expf(-x));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gate_up_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ chosen, const T* __restrict__ w_gu,
-                   T* __restrict__ hidden, int d, int top, int E, int F) {
+                   T* __restrict__ hidden, int d, int top, int E, int F, int act) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     const int pair = blockIdx.x, r = pair / top;
@@ -173,9 +193,23 @@ moe_gate_up_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ cho
     const bool vec = d % Vec16<T>::N == 0 && ((uintptr_t)w_gu | (uintptr_t)(x + (size_t)r * ldx)) % 16 == 0;
     fill_f32<T, true>(smem, x + (size_t)r * ldx, d, vec);
     __syncthreads();
-    const T* wg = w_gu + (size_t)e * 2 * F * d;
+    const T* wg = w_gu + (size_t)e * (act >= 0 ? 1 : 2) * F * d;
     const T* wu = wg + (size_t)F * d;
     const int j_end = min(F, (int)(blockIdx.y + 1) * MOE_COLS);
+    if (act >= 0) {                                        // no gate: two columns are two dot products
+        for (int j = blockIdx.y * MOE_COLS + 2 * warp; j < j_end; j += 2 * nw) {
+            const int j1 = min(j + 1, j_end - 1);
+            const T* const w[2] = {wg + (size_t)j * d, wg + (size_t)j1 * d};
+            const float* const x2[2] = {smem, smem};
+            float r[2];
+            warp_dots<T, 2>(w, x2, d, lane, vec, r);
+            if (lane == 0) {
+                hidden[(size_t)pair * F + j] = from_f32<T>(unit_act(r[0], act));
+                if (j1 != j) hidden[(size_t)pair * F + j1] = from_f32<T>(unit_act(r[1], act));
+            }
+        }
+        return;
+    }
     // a warp takes two columns at a time: their gate and up rows are four dot products in flight
     for (int j = blockIdx.y * MOE_COLS + 2 * warp; j < j_end; j += 2 * nw) {
         const int j1 = min(j + 1, j_end - 1);
@@ -252,7 +286,7 @@ int set_smem(K kernel, size_t bytes, const char* what) {
 
 TIS_API int tis_moe_route(int dtype, const void* x, int ldx, const float* wr, const float* corr, const float* w_sg,
                           int n, int d, int E, int groups, int keep, int top, float weight_eps, int* chosen,
-                          float* weights, float* shared_gate, cudaStream_t stream) {
+                          float* weights, float* shared_gate, int score_kind, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (d <= 0 || E <= 0 || top <= 0 || top > E || groups < 0 || (groups > 0 && (E % groups || keep <= 0 || keep > groups ||
         top > E / groups * keep)) || (w_sg != nullptr && shared_gate == nullptr)) {
@@ -264,13 +298,13 @@ TIS_API int tis_moe_route(int dtype, const void* x, int ldx, const float* wr, co
         const int st = set_smem(moe_route_kernel<T>, smem, "moe_route");
         if (st != TIS_OK) return st;
         tis_launch(moe_route_kernel<T>, dim3(n), dim3(2 * MOE_THREADS), smem, stream, (const T*)x, ldx, wr, corr, w_sg, d, E,
-                   groups, keep, top, weight_eps, chosen, weights, shared_gate);
+                   groups, keep, top, weight_eps, chosen, weights, shared_gate, score_kind);
     });
     return tis_check_launch("moe_route");
 }
 
 TIS_API int tis_moe_gate_up(int dtype, const void* x, int ldx, const int* chosen, const void* w_gu, void* hidden, int n,
-                            int d, int top, int E, int F, cudaStream_t stream) {
+                            int d, int top, int E, int F, int act, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (d <= 0 || top <= 0 || E <= 0 || F <= 0) {
         tis_set_error("moe_gate_up: width %d, top %d, %d experts of %d hidden", d, top, E, F);
@@ -281,7 +315,7 @@ TIS_API int tis_moe_gate_up(int dtype, const void* x, int ldx, const int* chosen
         const int st = set_smem(moe_gate_up_kernel<T>, smem, "moe_gate_up");
         if (st != TIS_OK) return st;
         tis_launch(moe_gate_up_kernel<T>, dim3(n * top, (F + MOE_COLS - 1) / MOE_COLS), dim3(MOE_THREADS), smem, stream,
-                   (const T*)x, ldx, chosen, (const T*)w_gu, (T*)hidden, d, top, E, F);
+                   (const T*)x, ldx, chosen, (const T*)w_gu, (T*)hidden, d, top, E, F, act);
     });
     return tis_check_launch("moe_gate_up");
 }
@@ -373,12 +407,13 @@ __device__ __forceinline__ void g_cp_async16(void* smem, const void* gmem) {
 
 // C[tile rows][n0 .. n0 + 64) = A . W[e]^T over K.  GATED: W[e] holds N gate rows and then N up rows, and C = silu(gate) *
 // up; else W[e] holds N rows.  GATHER: row i of the tile is row sorted_pair[.] / top of A (a token's input; places
-// without a pair: zeros); else row i of the tile is row tile * 64 + i of A (the sorted hidden rows).
+// without a pair: zeros); else row i of the tile is row tile * 64 + i of A (the sorted hidden rows).  act >= 0 (not GATED):
+// C = act(A . W[e]^T), the first product of units without a gate.
 template <bool GATED, bool GATHER>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ sorted_pair, int top,
                    const int* __restrict__ tile_expert, const bf16* __restrict__ W, size_t expert_stride,
-                   bf16* __restrict__ C, int ldc, int N, int K) {
+                   bf16* __restrict__ C, int ldc, int N, int K, int act) {
     constexpr int BROWS = GATED ? 2 * GT_COLS : GT_COLS;
     __shared__ __align__(16) bf16 As[GT_STAGES][GT_ROWS][GT_LD];
     __shared__ __align__(16) bf16 Bs[GT_STAGES][BROWS][GT_LD];
@@ -472,6 +507,9 @@ moe_grouped_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ 
                 if (GATED) {
                     v0 = v0 / (1.f + __expf(-v0)) * acc[GATED ? 1 : 0][mi][n][2 * half];
                     v1 = v1 / (1.f + __expf(-v1)) * acc[GATED ? 1 : 0][mi][n][2 * half + 1];
+                } else if (act >= 0) {
+                    v0 = unit_act(v0, act);
+                    v1 = unit_act(v1, act);
                 }
                 if (col + 1 < N) *reinterpret_cast<__nv_bfloat162*>(C + row * ldc + col) = __floats2bfloat162_rn(v0, v1);
                 else if (col < N) C[row * ldc + col] = __float2bfloat16_rn(v0);
@@ -528,13 +566,14 @@ int tis_moe_combine_launch(const void* y, int ldy, const int* pair_place, const 
 // Tiles of 64 sorted rows that `pairs` (token, choice) pairs over E experts can need at most.
 TIS_API int tis_moe_grouped_tiles(int pairs, int E) { return (pairs + GT_ROWS - 1) / GT_ROWS + E; }
 
-// The experts' products for many rows in bfloat16.  x (n, d) with row stride ldx; w_gu (E, 2, F, d); w_down (E, d, F);
+// The experts' products for many rows in bfloat16.  x (n, d) with row stride ldx; w_gu (E, 2, F, d), or (E, F, d) with
+// act >= 0 (units without a gate); w_down (E, d, F);
 // scratch: sorted_pair and hidden / y rows for tis_moe_grouped_tiles(n * top, E) * 64 places, pair_place n * top,
 // tile_expert that many tiles.  d and F multiples of 32; ldx, lds multiples of 8 and even; operands 16-byte aligned.
 TIS_API int tis_moe_grouped(const void* x, int ldx, const int* chosen, const float* weights, const void* w_gu,
                             const void* w_down, const void* shared, int lds, const float* shared_gate, void* out,
                             int* sorted_pair, int* pair_place, int* tile_expert, void* hidden, void* y, int n, int d,
-                            int top, int E, int F, cudaStream_t stream) {
+                            int top, int E, int F, int act, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (d <= 0 || F <= 0 || d % GT_BK || F % GT_BK || ldx % 8 || lds % 2 || E <= 0 || E > 4096 || top <= 0 ||
         ((uintptr_t)x | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)hidden | (uintptr_t)y) % 16 ||
@@ -546,14 +585,19 @@ TIS_API int tis_moe_grouped(const void* x, int ldx, const int* chosen, const flo
     const int pairs = n * top, tiles = tis_moe_grouped_tiles(pairs, E);
     int st = tis_moe_sort_launch(chosen, pairs, E, GT_ROWS, sorted_pair, tiles * GT_ROWS, pair_place, tile_expert, tiles, stream);
     if (st != TIS_OK) return st;
-    tis_launch(moe_grouped_kernel<true, true>, dim3(tiles, (F + GT_COLS - 1) / GT_COLS), dim3(128), 0, stream, (const bf16*)x,
-               ldx, (const int*)sorted_pair, top, (const int*)tile_expert, (const bf16*)w_gu, (size_t)2 * F * d, (bf16*)hidden, F,
-               F, d);
+    if (act >= 0)
+        tis_launch(moe_grouped_kernel<false, true>, dim3(tiles, (F + GT_COLS - 1) / GT_COLS), dim3(128), 0, stream,
+                   (const bf16*)x, ldx, (const int*)sorted_pair, top, (const int*)tile_expert, (const bf16*)w_gu, (size_t)F * d,
+                   (bf16*)hidden, F, F, d, act);
+    else
+        tis_launch(moe_grouped_kernel<true, true>, dim3(tiles, (F + GT_COLS - 1) / GT_COLS), dim3(128), 0, stream,
+                   (const bf16*)x, ldx, (const int*)sorted_pair, top, (const int*)tile_expert, (const bf16*)w_gu,
+                   (size_t)2 * F * d, (bf16*)hidden, F, F, d, -1);
     st = tis_check_launch("moe_grouped_gate_up");
     if (st != TIS_OK) return st;
     tis_launch(moe_grouped_kernel<false, false>, dim3(tiles, (d + GT_COLS - 1) / GT_COLS), dim3(128), 0, stream,
                (const bf16*)hidden, F, (const int*)sorted_pair, top, (const int*)tile_expert, (const bf16*)w_down, (size_t)d * F,
-               (bf16*)y, d, d, F);
+               (bf16*)y, d, d, F, -1);
     st = tis_check_launch("moe_grouped_down");
     if (st != TIS_OK) return st;
     return tis_moe_combine_launch(y, d, pair_place, weights, shared, lds, shared_gate, out, n, d, top, stream);

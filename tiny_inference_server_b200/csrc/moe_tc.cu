@@ -30,7 +30,14 @@ struct MoeTcParams {
     int tiles_m, tiles_n;
     const int* tile_expert;
     int* fault;
+    int act;                // not gated: -1 none, else the activation of the output (0 relu^2, 1 gelu (tanh), 2 silu)
 };
+
+__device__ __forceinline__ float tile_act(float x, int kind) {
+    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == 1) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.f + __expf(-x));
+}
 
 template <int BN, int STAGES, bool GATED>
 __global__ void __launch_bounds__(NTH, 1)
@@ -139,6 +146,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     tmem_ld32(taddr + BH + c * 32, u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) g[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+                } else if (p.act >= 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) g[i] = tile_act(g[i], p.act);
                 }
                 bf16* o = p.out + row * p.ldo + n0 + c * 32;
 #pragma unroll
@@ -206,12 +216,12 @@ int tis_moe_combine_launch(const void* y, int ldy, const int* pair_place, const 
 TIS_API int tis_moe_tc_tiles(int pairs, int E) { return (pairs + BM - 1) / BM + E; }
 
 // The experts' products for many rows in bfloat16 on the tcgen05 tensor cores.  x (n, d) with row stride ldx; w_gu
-// (E, 2, F, d); w_down (E, d, F); scratch for T = tis_moe_tc_tiles(n * top, E) tiles: sorted_pair T * 128, pair_place
+// (E, 2, F, d), or (E, F, d) with act >= 0 (units without a gate, the activation on the first product); w_down (E, d, F); scratch for T = tis_moe_tc_tiles(n * top, E) tiles: sorted_pair T * 128, pair_place
 // n * top, tile_expert T, xs (T * 128, d), hidden (T * 128, F), y (T * 128, d).  d and F multiples of 64.
 TIS_API int tis_moe_grouped_tc(const void* x, int ldx, const int* chosen, const float* weights, const void* w_gu,
                                const void* w_down, const void* shared, int lds, const float* shared_gate, void* out,
                                int* sorted_pair, int* pair_place, int* tile_expert, void* xs, void* hidden, void* y, int n,
-                               int d, int top, int E, int F, int* fault, cudaStream_t stream) {
+                               int d, int top, int E, int F, int act, int* fault, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (d <= 0 || F <= 0 || d % BK || F % BK || ldx % 8 || lds % 2 || E <= 0 || E > 4096 || top <= 0 ||
         ((uintptr_t)x | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)xs | (uintptr_t)hidden | (uintptr_t)y) % 16 ||
@@ -235,7 +245,20 @@ TIS_API int tis_moe_grouped_tc(const void* x, int ldx, const int* chosen, const 
     p.tiles_n = 0;
     // gate and up with the gating: K = d, the stacked matrix has E * 2F rows of d elements
     p.out = static_cast<bf16*>(hidden); p.ldo = F; p.N = F; p.K = d; p.rows_per_expert = 2 * F; p.up_offset = F;
-    if (F >= 128) {
+    p.act = -1;
+    if (act >= 0) {
+        // units without a gate: one matrix of F rows an expert, the activation in the epilogue
+        p.rows_per_expert = F; p.up_offset = 0; p.act = act;
+        if (F >= 256) {
+            if (!tensor_map(xs, d, rows, d, BM, true, &ma) || !tensor_map(w_gu, d, (long long)E * F, d, 256, true, &mb))
+                return TIS_CUDA_ERROR;
+            st = launch<256, 4, false>(ma, mb, p, stream);
+        } else {
+            if (!tensor_map(xs, d, rows, d, BM, true, &ma) || !tensor_map(w_gu, d, (long long)E * F, d, 128, true, &mb))
+                return TIS_CUDA_ERROR;
+            st = launch<128, 6, false>(ma, mb, p, stream);
+        }
+    } else if (F >= 128) {
         if (!tensor_map(xs, d, rows, d, BM, true, &ma) || !tensor_map(w_gu, d, (long long)E * 2 * F, d, 128, true, &mb))
             return TIS_CUDA_ERROR;
         st = launch<256, 4, true>(ma, mb, p, stream);
@@ -246,7 +269,7 @@ TIS_API int tis_moe_grouped_tc(const void* x, int ldx, const int* chosen, const 
     }
     if (st != TIS_OK) return st;
     // down: K = F, the stacked matrix has E * d rows of F elements
-    p.out = static_cast<bf16*>(y); p.ldo = d; p.N = d; p.K = F; p.rows_per_expert = d; p.up_offset = 0;
+    p.out = static_cast<bf16*>(y); p.ldo = d; p.N = d; p.K = F; p.rows_per_expert = d; p.up_offset = 0; p.act = -1;
     if (d >= 256) {
         if (!tensor_map(hidden, F, rows, F, BM, true, &ma) || !tensor_map(w_down, F, (long long)E * d, F, 256, true, &mb))
             return TIS_CUDA_ERROR;

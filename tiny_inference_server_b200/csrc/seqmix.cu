@@ -12,8 +12,8 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------------------------
-// y[r, c] = (residual ? x[r, c] : 0) + sum_j w[j, c] * x(t - taps + 1 + j)[c], optionally through silu (the weights
-// lie tap by tap: [taps][C]).
+// y[r, c] = (residual ? x[r, c] : 0) + bias[c] + sum_j w[j, c] * x(t - taps + 1 + j)[c], optionally through silu (the
+// weights lie tap by tap: [taps][C]; bias null: none).
 // x(t') of a position before this step's rows of the request comes from the request's state, which holds its
 // last taps-1 inputs (oldest first, zero before the start of the sequence) and is brought up to date here.
 //
@@ -27,7 +27,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ state,
                    size_t state_stride, T* __restrict__ out, int ldo, const int* __restrict__ row_slot,
-                   const int* __restrict__ row_last, int n, int C, int taps, int residual, int act_silu) {
+                   const int* __restrict__ row_last, int n, int C, int taps, int residual, int act_silu,
+                   const float* __restrict__ bias) {
     pdl_launch_dependents();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int r = blockIdx.y;
@@ -41,6 +42,7 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w
     float wt[CONV_MAX_TAPS];
 #pragma unroll
     for (int j = 0; j < CONV_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)j * C + c] : 0.f;
+    const float b0 = bias != nullptr ? bias[c] : 0.f;
     pdl_wait();
     if (back == hist) {                               // every input is a row of this step (or there is no history)
         float acc = 0.f, cur = 0.f;
@@ -51,6 +53,7 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w
                 acc = fmaf(wt[j], cur, acc);
             }
         }
+        acc += b0;
         if (residual) acc += cur;
         if (act_silu) acc = acc / (1.f + expf(-acc));
         out[(size_t)r * ldo + c] = from_f32<T>(acc);
@@ -69,7 +72,7 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w
 #pragma unroll
         for (int k = 0; k < CONV_MAX_TAPS; ++k)
             if (k < hist) acc = fmaf(wt[k], h[k], acc);
-        acc = fmaf(wt[hist], cur, acc);
+        acc = fmaf(wt[hist], cur, acc) + b0;
         if (residual) acc += cur;
         if (act_silu) acc = acc / (1.f + expf(-acc));
         out[(size_t)(r + i) * ldo + c] = from_f32<T>(acc);
@@ -96,7 +99,8 @@ template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
 causal_conv_vec_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ state,
                        size_t state_stride, T* __restrict__ out, int ldo, const int* __restrict__ row_slot,
-                       const int* __restrict__ row_last, int n, int C, int residual, int act_silu) {
+                       const int* __restrict__ row_last, int n, int C, int residual, int act_silu,
+                       const float* __restrict__ bias) {
     constexpr int N = Vec16<T>::N, HIST = TAPS - 1;
     pdl_launch_dependents();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * N;
@@ -115,10 +119,14 @@ causal_conv_vec_kernel(const T* __restrict__ x, int ldx, const float* __restrict
             const float4 v = *reinterpret_cast<const float4*>(w + (size_t)j * C + c + e);
             wt[e][j] = v.x; wt[e + 1][j] = v.y; wt[e + 2][j] = v.z; wt[e + 3][j] = v.w;
         }
+    float b0[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) b0[e] = bias != nullptr ? bias[c + e] : 0.f;
     pdl_wait();
     auto finish = [&](float (&acc)[N], const float (&cur)[N], size_t row) {
 #pragma unroll
         for (int e = 0; e < N; ++e) {
+            acc[e] += b0[e];
             if (residual) acc[e] += cur[e];
             if (act_silu) acc[e] = acc[e] / (1.f + expf(-acc[e]));
         }
@@ -178,17 +186,17 @@ causal_conv_vec_kernel(const T* __restrict__ x, int ldx, const float* __restrict
 template <typename T, int TAPS>
 static void launch_causal_conv_vec(const T* x, int ldx, const float* w, float* state, size_t state_stride, T* out, int ldo,
                                    const int* row_slot, const int* row_last, int n, int C, int residual, int act_silu,
-                                   cudaStream_t stream) {
+                                   const float* bias, cudaStream_t stream) {
     constexpr int N = Vec16<T>::N;
     const int vecs = C / N;
     const int threads = vecs >= 128 ? 128 : (vecs + 31) / 32 * 32;
     tis_launch(causal_conv_vec_kernel<T, TAPS>, dim3((vecs + threads - 1) / threads, n), dim3(threads), 0, stream, x, ldx, w,
-               state, state_stride, out, ldo, row_slot, row_last, n, C, residual, act_silu);
+               state, state_stride, out, ldo, row_slot, row_last, n, C, residual, act_silu, bias);
 }
 
 TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, float* state, size_t state_stride,
                             void* out, int ldo, const int* row_slot, const int* row_last, int n, int C, int taps,
-                            int residual, int act_silu, cudaStream_t stream) {
+                            int residual, int act_silu, const float* bias, cudaStream_t stream) {
     if (n <= 0 || C <= 0) return TIS_OK;
     if (taps < 1 || taps > CONV_MAX_TAPS) {
         tis_set_error("causal_conv: %d taps; this kernel takes 1..%d", taps, CONV_MAX_TAPS);
@@ -204,7 +212,7 @@ TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, f
 #define TIS_CONV_CASE(K)                                                                                               \
     case K:                                                                                                            \
         TIS_DISPATCH_DTYPE(dtype, T, launch_causal_conv_vec<T, K>((const T*)x, ldx, w, state, state_stride, (T*)out,   \
-            ldo, row_slot, row_last, n, C, residual, act_silu, stream));                                               \
+            ldo, row_slot, row_last, n, C, residual, act_silu, bias, stream));                                               \
         break;
         switch (taps) {
             TIS_CONV_CASE(2)
@@ -217,7 +225,7 @@ TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, f
     }
     TIS_DISPATCH_DTYPE(dtype, T,
         tis_launch(causal_conv_kernel<T>, dim3((C + 127) / 128, n), dim3(128), 0, stream, (const T*)x, ldx, w, state,
-                   state_stride, (T*)out, ldo, row_slot, row_last, n, C, taps, residual, act_silu));
+                   state_stride, (T*)out, ldo, row_slot, row_last, n, C, taps, residual, act_silu, bias));
     return tis_check_launch("causal_conv");
 }
 
@@ -785,7 +793,14 @@ __device__ __forceinline__ float gate_f(float x, int act) { const float s = 1.f 
 // gate's projection, `dt_bias` its bias and `A_log` a lower bound per head and key channel, f = low + (1 - low) *
 // sigmoid(a + bias), S <- diag(f) S + (1 - f) v^T, o = S^T silu(q): the key is 1 - f, there is no key projection (a
 // row of `qkv` holds the queries and then the values), no unit norms and no correction towards v
-enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2, DECAY_FORGET_GATE = 3 };
+// or (DECAY_LOG_SIGMOID) a gate per head and key channel raised to a power: with `a_in` the gate's projection, `dt_bias`
+// its bias and `A_log` the power itself per head (1 / tau), g = sigmoid(a + bias)^power = exp(-power * softplus(-(a + bias))),
+// S <- diag(g) S + k v^T, o = S^T (q * q_scale): gated linear attention, no unit norms, no correction
+// or (DECAY_STEP) a step size per head and token: with `a_in` (n, H) its projection and `dt_bias` (H) its bias,
+// dt = softplus(a + bias), S <- exp(-exp(A_log[head]) * dt) S + k (dt v)^T, o = S^T q: a selective state space in its
+// recurrent form (k is the input matrix B, q the output matrix C, v the head's inputs); the outputs leave unnormalised
+enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2, DECAY_FORGET_GATE = 3, DECAY_LOG_SIGMOID = 4,
+       DECAY_STEP = 5 };
 
 template <typename T, int DIM>
 __global__ void __launch_bounds__(DIM > 0 ? 256 : 1024)
@@ -814,8 +829,10 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     float* S_sh = betas + DELTA_CHUNK;                  // [k_dim][v_dim] when DIM == 0
     const bool plain = decay_mode == DECAY_CONSTANT;
     const bool forget = decay_mode == DECAY_FORGET_GATE;
-    const bool corrects = !plain && !forget;            // the delta rule proper: the state is corrected towards v
-    const float decay_rate = plain ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
+    const bool gated = decay_mode == DECAY_LOG_SIGMOID;
+    const bool stepped = decay_mode == DECAY_STEP;
+    const bool corrects = !plain && !forget && !gated && !stepped;   // the delta rule proper: the state is corrected towards v
+    const float decay_rate = (plain || gated) ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * k_dim * v_dim;
     // a state too large for shared memory is walked where it lies (DIM == 0 only): a thread touches its own column alone
     const bool in_place = DIM == 0 && state_in_place != 0;
@@ -848,6 +865,20 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                 }
                 for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = to_f32(row[v_off + j]);
                 if (lane == 0) betas[t] = 1.f;
+                continue;
+            }
+            if (gated || stepped) {
+                const size_t rr = (size_t)(r0 + c0 + t);
+                const float dtv = stepped ? softplus_f(to_f32(a_in[rr * lda + head]) + dt_bias[head]) : 1.f;
+                const float whole = expf(-decay_rate * dtv);
+                for (int i = lane; i < k_dim; i += 32) {
+                    qs[t * k_dim + i] = to_f32(row[q_off + i]) * q_scale;
+                    ks[t * k_dim + i] = to_f32(row[k_off + i]);
+                    gs[t * k_dim + i] = stepped ? whole : expf(-decay_rate * softplus_f(
+                        -(to_f32(a_in[rr * lda + (size_t)head * k_dim + i]) + dt_bias[head * k_dim + i])));
+                }
+                for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = to_f32(row[v_off + j]);
+                if (lane == 0) betas[t] = dtv;
                 continue;
             }
             float sq = 0.f, sk = 0.f;
@@ -896,7 +927,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S[i] *= gt[i];
                         dot = fmaf(S[i], kt[i], dot);
                     }
-                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : vs[t * v_dim + tid];
+                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : betas[t] * vs[t * v_dim + tid];
 #pragma unroll
                     for (int i = 0; i < REG; ++i) {
                         S[i] = fmaf(kt[i], u, S[i]);
@@ -908,7 +939,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S_sh[i * v_dim + tid] = s;
                         dot = fmaf(s, kt[i], dot);
                     }
-                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : vs[t * v_dim + tid];
+                    const float u = corrects ? betas[t] * (vs[t * v_dim + tid] - dot) : betas[t] * vs[t * v_dim + tid];
                     for (int i = 0; i < k_dim; ++i) {
                         const float s = fmaf(kt[i], u, S_sh[i * v_dim + tid]);
                         S_sh[i * v_dim + tid] = s;
@@ -959,7 +990,8 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
 // values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
 // unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
 // MODE 0: the delta rule (decays from projections, the state corrected towards v); 1: a constant decay per head,
-// silu on q, k and v, no correction; 2: the forget gate of DECAY_FORGET_GATE.
+// silu on q, k and v, no correction; 2: the forget gate of DECAY_FORGET_GATE; 3: the powered gate of DECAY_LOG_SIGMOID;
+// 4: the step size of DECAY_STEP.
 template <typename T, int DL, int LANES, int COLS, int MODE>
 __global__ void __launch_bounds__(COLS * LANES)
 delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
@@ -990,8 +1022,8 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int col = tid / LANES, part = tid % LANES;
     // PLAIN: the decay is a constant per head and the state takes k v^T as it is, so the walk needs neither the decays of
     // the chunk nor the first of its two sums over the lanes of a column
-    constexpr bool plain = MODE == 1, forget = MODE == 2;
-    const float decay_rate = plain ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
+    constexpr bool plain = MODE == 1, forget = MODE == 2, gated = MODE == 3, stepped = MODE == 4;
+    const float decay_rate = (plain || gated) ? A_log[head] : (forget ? 0.f : expf(A_log[head]));
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
     float S[DL];
     pdl_wait();
@@ -1000,8 +1032,9 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = (forget ? 1 : 2) * G * KDIM + head * v_dim + col0;
     const int nv = H * v_dim;
     const int pt = tid / PT, sub = tid % PT;
-    const size_t a_at = decay_mode == DECAY_PER_HEAD ? (size_t)head : (size_t)head * KDIM;
-    const int a_step = decay_mode == DECAY_PER_HEAD ? 0 : 1;
+    const bool per_head = decay_mode == DECAY_PER_HEAD || decay_mode == DECAY_STEP;
+    const size_t a_at = per_head ? (size_t)head : (size_t)head * KDIM;
+    const int a_step = per_head ? 0 : 1;
     float rq[CH], rk[CH], ra[CH], rv[VPT], rb = 0.f;
     auto fetch = [&](int c0) {
         const bool live = c0 + pt < rows;
@@ -1015,7 +1048,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
         }
 #pragma unroll
         for (int i = 0; i < VPT; ++i) rv[i] = live ? to_f32(row[v_off + sub * VPT + i]) : 0.f;
-        rb = (live && sub == 0 && !plain && !forget) ? to_f32(b_in[rr * ldb + head]) : 0.f;
+        rb = (live && sub == 0 && MODE == 0) ? to_f32(b_in[rr * ldb + head]) : 0.f;
     };
     float bias[CH], low[CH];
 #pragma unroll
@@ -1046,6 +1079,10 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
                     qs[pt][at] = silu_f(rq[i]);
                     ks[pt][at] = (1.f - low[i]) * open;                          // 1 - f
                     gs[pt][at] = low[i] + (1.f - low[i]) * (1.f - open);         // f
+                } else if (gated || stepped) {
+                    qs[pt][at] = rq[i] * q_scale;
+                    ks[pt][at] = rk[i];
+                    gs[pt][at] = expf(-decay_rate * softplus_f(gated ? -(ra[i] + bias[i]) : ra[i] + bias[i]));
                 } else {
                     qs[pt][at] = plain ? silu_f(rq[i]) : rq[i] * fq;
                     ks[pt][at] = plain ? silu_f(rk[i]) : rk[i] * fk;
@@ -1054,7 +1091,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) vs[pt][sub * VPT + i] = plain ? silu_f(rv[i]) : rv[i];
-            if (sub == 0) betas[pt] = 1.f / (1.f + expf(-rb));
+            if (sub == 0) betas[pt] = stepped ? softplus_f(ra[0] + bias[0]) : 1.f / (1.f + expf(-rb));
         }
         __syncthreads();
         if (c0 + DELTA_CHUNK < rows) fetch(c0 + DELTA_CHUNK);
@@ -1097,9 +1134,10 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             if (plain) {
 #pragma unroll
                 for (int i = 0; i < DL; ++i) S[i] *= decay_rate;
-            } else if (forget) {
+            } else if (forget || gated || stepped) {
 #pragma unroll
                 for (int i = 0; i < DL / 2; ++i) { S[2 * i] *= gc[i].x; S[2 * i + 1] *= gc[i].y; }
+                if (stepped) u = bc * vc;
             } else {
 #pragma unroll
                 for (int i = 0; i < DL / 2; ++i) {
@@ -1210,12 +1248,20 @@ static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb,
         tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 2>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
                    lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
                    decay_mode);
+    else if (decay_mode == DECAY_LOG_SIGMOID)
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 3>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+                   lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
+                   decay_mode);
+    else if (decay_mode == DECAY_STEP)
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 4>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+                   lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
+                   decay_mode);
     else
         tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, 0>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
                    lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
                    decay_mode);
     int st = tis_check_launch("delta_rule");
-    if (st != TIS_OK) return st;
+    if (st != TIS_OK || decay_mode == DECAY_STEP) return st;      // DECAY_STEP: the caller gates and normalises `o_raw`
     if (decay_mode == DECAY_CONSTANT) {
         tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(256), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
                    row_slot, H * v_dim);
@@ -1248,7 +1294,8 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
         cudaFuncSetAttribute(delta_rule_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     tis_launch(delta_rule_kernel<T, DIM>, dim3(H, n), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
                A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, out, ldo, row_slot, row_last, H, G,
-               k_dim, v_dim, decay_mode, gate_act, decay_mode == DECAY_CONSTANT ? o_raw : (float*)nullptr, in_place);
+               k_dim, v_dim, decay_mode, gate_act,
+               (decay_mode == DECAY_CONSTANT || decay_mode == DECAY_STEP) ? o_raw : (float*)nullptr, in_place);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK || decay_mode != DECAY_CONSTANT) return st;
     tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(256), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
@@ -1270,8 +1317,8 @@ static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const voi
                                    int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, int decay_mode,
                                    int gate_act, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
-    if (decay_mode < DECAY_PER_CHANNEL || decay_mode > DECAY_FORGET_GATE || gate_act < 0 || gate_act > 1 ||
-        (decay_mode == DECAY_CONSTANT && o_raw == nullptr)) {
+    if (decay_mode < DECAY_PER_CHANNEL || decay_mode > DECAY_STEP || gate_act < 0 || gate_act > 1 ||
+        ((decay_mode == DECAY_CONSTANT || decay_mode == DECAY_STEP) && o_raw == nullptr)) {
         tis_set_error("delta_rule: decay mode %d, gate activation %d%s", decay_mode, gate_act,
                       o_raw == nullptr ? ", no scratch for the outputs" : "");
         return TIS_BAD_SIZE;
@@ -1371,4 +1418,32 @@ TIS_API int tis_forget_gate_recurrence(int dtype, const void* qv, int ld, const 
     return matrix_state_recurrence(dtype, qv, ld, nullptr, 0, f_in, ldf, nullptr, 0, lower, f_bias, norm_w, eps, 0.f, 1.f,
                                    state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, H, k_dim, v_dim, narrow,
                                    seg_row0, segments, DECAY_FORGET_GATE, 0, stream);
+}
+
+// Gated linear attention (DECAY_LOG_SIGMOID): a row of `qkv` holds the queries and keys of H heads (k_dim each) and the
+// values of H heads (v_dim each); `a_in` (n, H * k_dim) the gate's projection, `a_bias` (H * k_dim) its bias, `power` (H)
+// the exponent of the gate.  alpha = sigmoid(a + bias)^power; S <- diag(alpha) S + k v^T; o = S^T (q * q_scale); per head
+// out = o / sqrt(mean(o^2) + eps) * norm_w (v_dim weights, the same for every head) * act(gate).  `o_raw`: n * H * v_dim
+// floats of scratch where tis_delta_rule_splits.
+TIS_API int tis_gated_linear_attention(int dtype, const void* qkv, int ld, const void* a_in, int lda, const float* power,
+                                       const float* a_bias, const void* gate, int ldg, const float* norm_w, float eps,
+                                       float q_scale, float* state, size_t state_stride, void* out, int ldo, float* o_raw,
+                                       const int* row_slot, const int* row_last, int n, int H, int k_dim, int v_dim,
+                                       int narrow, const int* seg_row0, int segments, int gate_act, cudaStream_t stream) {
+    return matrix_state_recurrence(dtype, qkv, ld, nullptr, 0, a_in, lda, gate, ldg, power, a_bias, norm_w, eps, 0.f, q_scale,
+                                   state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, H, k_dim, v_dim, narrow,
+                                   seg_row0, segments, DECAY_LOG_SIGMOID, gate_act, stream);
+}
+
+// A selective state space in its recurrent form (DECAY_STEP): a row of `cbx` holds the output matrices C and then the input
+// matrices B of G groups (`state_dim` each) and then the inputs x of H heads (v_dim each); `dt_in` (n, H) the step's
+// projection, `dt_bias`, `A_log` (H).  dt = softplus(dt_in + dt_bias); S <- exp(-exp(A_log) dt) S + B (dt x)^T;
+// o_raw = S^T C, 32-bit, (n, H * v_dim): what follows (a skip, a gate, a norm) is the caller's.
+TIS_API int tis_state_space_scan(int dtype, const void* cbx, int ld, const void* dt_in, int ldd, const float* A_log,
+                                 const float* dt_bias, float* state, size_t state_stride, float* o_raw, const int* row_slot,
+                                 const int* row_last, int n, int H, int G, int state_dim, int v_dim, int narrow,
+                                 const int* seg_row0, int segments, cudaStream_t stream) {
+    return matrix_state_recurrence(dtype, cbx, ld, nullptr, 0, dt_in, ldd, nullptr, 0, A_log, dt_bias, nullptr, 0.f, 0.f, 1.f,
+                                   state, state_stride, nullptr, 0, o_raw, row_slot, row_last, n, H, G, state_dim, v_dim,
+                                   narrow, seg_row0, segments, DECAY_STEP, 0, stream);
 }

@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 10
+ABI_VERSION = 11
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -849,9 +849,10 @@ def gemm_act(a, w: torch.Tensor, kind: str) -> torch.Tensor:
 
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
-                row_last: torch.Tensor, residual: bool = False, silu: bool = False) -> torch.Tensor:
-    """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + sum_j weight[j, c] *
-    x(t - taps + 1 + j)[c]``, through silu if asked.  ``x`` (n, C) with a free row stride; ``weight`` (taps, C)
+                row_last: torch.Tensor, residual: bool = False, silu: bool = False,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + (bias[c] if given) +
+    sum_j weight[j, c] * x(t - taps + 1 + j)[c]``, through silu if asked (``bias`` (C,) float32).  ``x`` (n, C) with a free row stride; ``weight`` (taps, C)
     float32 (tap by tap, so that neighbouring channels are neighbours in memory); ``state`` (slots, taps - 1, C) float32 (a view with a free slot stride): the last inputs of every
     request, oldest first, zero before the start of a sequence; read for the rows whose history lies before this
     step and brought up to date."""
@@ -862,7 +863,7 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out:
         raise KernelError(f"causal_conv: weights {tuple(weight.shape)} for {c} channels (wanted contiguous (taps, channels))")
     _check(lib.tis_causal_conv(_dt(x), _p(x), x.stride(0), _p(weight), _p(state), ctypes.c_size_t(state.stride(0)),
                                _p(out), out.stride(0), _p(row_slot), _p(row_last), n, c, taps, int(residual), int(silu),
-                               _stream()), lib)
+                               _p(bias), _stream()), lib)
     return out
 
 
@@ -1160,16 +1161,140 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
     return out
 
 
+def gated_linear_attention(qkv: torch.Tensor, a_in: torch.Tensor, power: torch.Tensor, a_bias: torch.Tensor,
+                           gate: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float, q_scale: float,
+                           state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
+                           num_heads: int, k_dim: int, v_dim: int, requests: Optional[int] = None, segments=None,
+                           gate_act: str = "silu") -> torch.Tensor:
+    """Linear attention with a gate per head and key channel over the rows of every request, from and into ``state``
+    (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of ``qkv``: queries and keys of H heads
+    (k_dim each), values of H heads (v_dim each); ``a_in`` (n, H * k_dim) the gate's projection, ``a_bias`` (H * k_dim)
+    its bias, ``power`` (H,) its exponent.  ``alpha = sigmoid(a_in + a_bias) ** power``; ``S <- diag(alpha) S + k v^T``;
+    ``o = S^T (q * q_scale)``; per head ``out = o / rms(o) * norm_weight * act(gate)`` (v_dim weights shared by the
+    heads).  Gate, state and norm are 32-bit.  ``requests`` and ``segments`` as for ``delta_rule``."""
+    lib = library()
+    n = qkv.shape[0]
+    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    raw = None
+    if lib.tis_delta_rule_splits(k_dim, v_dim):
+        raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qkv.device)
+        global launches
+        launches += 1
+    _check(lib.tis_gated_linear_attention(_dt(qkv), _p(qkv), qkv.stride(0), _p(a_in), a_in.stride(0), _p(power), _p(a_bias),
+                                          _p(gate), gate.stride(0) if gate is not None else 0, _p(norm_weight), _f(eps),
+                                          _f(q_scale), _p(state), ctypes.c_size_t(state.stride(0)), _p(out), out.stride(0),
+                                          _p(raw), _p(row_slot), _p(row_last), n, num_heads, k_dim, v_dim, int(narrow),
+                                          _p(segments[0] if segments is not None else None),
+                                          int(segments[1]) if segments is not None else 0, GATE_ACTS[gate_act], _stream()), lib)
+    return out
+
+
+def state_space_scan(cbx: torch.Tensor, dt_in: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                     state: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor, num_heads: int, groups: int,
+                     state_dim: int, v_dim: int, requests: Optional[int] = None, segments=None) -> torch.Tensor:
+    """A selective state space in its recurrent form over the rows of every request, from and into ``state`` (slots, H,
+    state_dim, v_dim) float32 (a view with a free slot stride).  A row of ``cbx``: the output matrices C and then the
+    input matrices B of ``groups`` groups (``state_dim`` each), then the inputs x of H heads (v_dim each); ``dt_in`` (n, H).
+    ``dt = softplus(dt_in + dt_bias)``; ``S <- exp(-exp(a_log) dt) S + B (dt x)^T``; returns ``S^T C`` (n, H * v_dim)
+    float32.  ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
+    lib = library()
+    n = cbx.shape[0]
+    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=cbx.device)
+    _check(lib.tis_state_space_scan(_dt(cbx), _p(cbx), cbx.stride(0), _p(dt_in), dt_in.stride(0), _p(a_log), _p(dt_bias),
+                                    _p(state), ctypes.c_size_t(state.stride(0)), _p(raw), _p(row_slot), _p(row_last), n,
+                                    num_heads, groups, state_dim, v_dim, int(narrow),
+                                    _p(segments[0] if segments is not None else None),
+                                    int(segments[1]) if segments is not None else 0, _stream()), lib)
+    return raw
+
+
+def skip_gate_group_norm(o_raw: torch.Tensor, x: torch.Tensor, skip: torch.Tensor, z: torch.Tensor, weight: torch.Tensor,
+                         groups: int, eps: float, out: torch.Tensor, row_slot: torch.Tensor, num_heads: int,
+                         v_dim: int) -> torch.Tensor:
+    """``y = (o_raw + skip[head] * x) * silu(z)`` over rows of H heads of v_dim elements, then the row in ``groups``
+    equal parts, each divided by its root mean square (eps inside the root), times ``weight``.  ``o_raw`` (n, H * v_dim)
+    float32; ``x``, ``z``, ``out`` (n, H * v_dim) with free row strides."""
+    lib = library()
+    n = o_raw.shape[0]
+    _check(lib.tis_skip_gate_group_norm(_dt(out), _p(o_raw), _p(x), x.stride(0), _p(skip), _p(z), z.stride(0), _p(weight),
+                                        int(groups), _f(eps), _p(out), out.stride(0), _p(row_slot), n, num_heads, v_dim,
+                                        _stream()), lib)
+    return out
+
+
+def embed_pairs(table: torch.Tensor, pairs: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor,
+                row_slot: torch.Tensor, row_last: torch.Tensor, prev: torch.Tensor, out: torch.Tensor, scale: float,
+                buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """``out[r] = table[token] * scale + pairs[(previous * mul_prev + token * mul_cur) % buckets]``; a sequence's first
+    token takes row ``buckets`` of ``pairs``.  ``prev`` (slots,) int32: every request's last token so far, read for a
+    request's first row of the step and brought up to date.  ``out`` is the float32 residual stream (n, d)."""
+    lib = library()
+    n, d = out.shape
+    _check(lib.tis_embed_pairs(_dt(table), _p(table), _p(pairs), _p(tokens), _p(positions), _p(row_slot), _p(row_last),
+                               _p(prev), _p(out), n, d, _f(scale), int(buckets), ctypes.c_longlong(mul_prev),
+                               ctypes.c_longlong(mul_cur), _stream()), lib)
+    return out
+
+
+def group_norm(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor], groups: int,
+               eps: float, w1: Optional[torch.Tensor], out1: Optional[torch.Tensor], w2: Optional[torch.Tensor] = None,
+               out2: Optional[torch.Tensor] = None, in_place: bool = False, dtype: Optional[torch.dtype] = None):
+    """``residual += delta_a + delta_b`` (each None: nothing), then the RMS norm in ``groups`` equal consecutive parts of
+    the sum (each part divided by its own root mean square, eps inside the root): ``out1 = normed * w1`` and, if asked,
+    ``out2 = normed * w2``.  ``in_place``: ``residual`` itself becomes ``normed * w1``.  ``w1`` None: only the sum."""
+    lib = library()
+    n, d = residual.shape
+    ref = next((t for t in (out1, out2, delta_a, delta_b) if t is not None), None)
+    code = _dt(ref) if ref is not None else (0 if dtype in (None, torch.float32) else 1)
+    _check(lib.tis_group_norm(code, _p(residual), _p(delta_a), _p(delta_b), int(groups), _f(eps), _p(w1), _p(out1), _p(w2),
+                              _p(out2), int(in_place), n, d, _stream()), lib)
+    return out1, out2
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float) -> torch.Tensor:
+    """``a * scale_a + b * scale_b`` (n, d), the sum formed in 32-bit; row strides free."""
+    lib = library()
+    n, d = a.shape
+    out = torch.empty((n, d), dtype=a.dtype, device=a.device)
+    _check(lib.tis_scaled_sum(_dt(a), _p(a), a.stride(0), _f(scale_a), _p(b), b.stride(0), _f(scale_b), _p(out), out.stride(0),
+                              n, d, _stream()), lib)
+    return out
+
+
+def rotate_tie_store(qk: torch.Tensor, num_heads: int, kv_heads: int, dim: int, rot: int, cos: torch.Tensor,
+                     sin: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                     positions: torch.Tensor, row_slot: torch.Tensor, page_size: int, fault: torch.Tensor) -> None:
+    """Between the projections and the cache of an attention whose values are its keys before rotation.  A row of ``qk``:
+    H query heads, then G key heads, ``dim`` elements each.  The first ``rot`` elements of every head are rotated by the
+    row's position (element i with i + rot / 2; ``cos``, ``sin`` (positions, rot / 2) float32): queries in place, keys into
+    the key rows of the row's page; the keys as projected go into the value rows."""
+    lib = library()
+    n = qk.shape[0]
+    kps, khs = _page_strides(k_pages, dim)
+    vps, vhs = _page_strides(v_pages, dim)
+    _check(lib.tis_rotate_tie_store(_dt(qk), _p(qk), qk.stride(0), num_heads, kv_heads, dim, rot, _p(cos), _p(sin),
+                                    _p(k_pages), kps, khs, _p(v_pages), vps, vhs, page_size, k_pages.shape[0],
+                                    _p(block_table), block_table.stride(0), _p(positions), _p(row_slot), _p(fault), n,
+                                    _stream()), lib)
+
+
 # ---------------------------------------------------------------------------------------
 # routed experts
 # ---------------------------------------------------------------------------------------
 
+#: how a router turns logits into choices and weights
+ROUTER_SCORES = {"sigmoid": 0, "softmax_chosen": 1}
+
+
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
-              w_shared_gate: Optional[torch.Tensor], groups: int, keep: int, top: int, weight_eps: float = 1e-20):
+              w_shared_gate: Optional[torch.Tensor], groups: int, keep: int, top: int, weight_eps: float = 1e-20,
+              scores: str = "sigmoid"):
     """The router of a mixture of experts, a row at a time, in 32-bit: ``s = sigmoid(w_router x)`` (E experts);
     choosing scores ``s + correction``; with ``groups`` > 0 only the experts of the ``keep`` groups (of E / groups
     neighbours) with the largest sum of their two best choosing scores can be chosen; the ``top`` largest choosing
-    scores win (the lower index on a tie); weights ``s`` of the chosen over their sum (+ ``weight_eps``).  Returns
+    scores win (the lower index on a tie); weights ``s`` of the chosen over their sum (+ ``weight_eps``).  ``scores``
+    ``"softmax_chosen"``: the logits themselves choose and the weights are the softmax over the chosen logits only.  Returns
     (chosen (n, top) int32, weights (n, top) float32, sigmoid(w_shared_gate . x) (n,) float32 or None)."""
     lib = library()
     n, d = x.shape
@@ -1179,20 +1304,21 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     shared = torch.empty((n,), dtype=torch.float32, device=x.device) if w_shared_gate is not None else None
     _check(lib.tis_moe_route(_dt(x), _p(x), x.stride(0), _p(w_router), _p(correction), _p(w_shared_gate), n, d, experts,
                              int(groups), int(keep), int(top), _f(weight_eps), _p(chosen), _p(weights), _p(shared),
-                             _stream()), lib)
+                             ROUTER_SCORES[scores], _stream()), lib)
     return chosen, weights, shared
 
 
-def moe_gate_up(x: torch.Tensor, chosen: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def moe_gate_up(x: torch.Tensor, chosen: torch.Tensor, w_gate_up: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
     """``hidden[r * top + k] = silu(Wg[e] x[r]) * (Wu[e] x[r])`` with ``e = chosen[r, k]``: ``w_gate_up`` (E, 2, F, d)
-    holds every expert's gate and up matrices (out, in); the result is (n * top, F) in the dtype of ``x``."""
+    holds every expert's gate and up matrices (out, in); the result is (n * top, F) in the dtype of ``x``.  ``act``
+    (``ACTIVATIONS``): units without a gate, ``hidden = act(Wu[e] x[r])`` with ``w_gate_up`` (E, F, d)."""
     lib = library()
     n, d = x.shape
     top = chosen.shape[1]
-    experts, _, hidden, _ = w_gate_up.shape
+    experts, hidden = w_gate_up.shape[0], w_gate_up.shape[-2]
     out = torch.empty((n * top, hidden), dtype=x.dtype, device=x.device)
     _check(lib.tis_moe_gate_up(_dt(x), _p(x), x.stride(0), _p(chosen), _p(w_gate_up), _p(out), n, d, top, experts, hidden,
-                               _stream()), lib)
+                               ACTIVATIONS[act] if act is not None else -1, _stream()), lib)
     return out
 
 
@@ -1261,15 +1387,17 @@ MOE_TC_MIN_PAIRS = int(os.environ.get("TIS_MOE_TC_MIN_PAIRS", "1024"))
 
 
 def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                shared: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor]) -> torch.Tensor:
+                shared: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor], act: Optional[str] = None) -> torch.Tensor:
     """``out[r] = sum_k weights[r, k] * unit(chosen[r, k])(x[r]) (+ shared_gate[r] * shared[r])`` with the gated units
-    ``unit(e)(x) = Wd[e] (silu(Wg[e] x) * (Wu[e] x))``: ``w_gate_up`` (E, 2, F, d), ``w_down`` (E, d, F).  Few rows, and
+    ``unit(e)(x) = Wd[e] (silu(Wg[e] x) * (Wu[e] x))``: ``w_gate_up`` (E, 2, F, d), ``w_down`` (E, d, F); or, with ``act``
+    (``ACTIVATIONS``), units without a gate, ``Wd[e] act(Wu[e] x)`` and ``w_gate_up`` (E, F, d).  Few rows, and
     float32: ``moe_gate_up`` and ``moe_down`` (a dot product per output element, the weights read where they lie).  Many
     bfloat16 rows: the rows are sorted by expert on the device and every expert's rows run as tiles on the tensor
     cores; nothing is read back, so either way the step can be captured in a graph."""
     n, d = x.shape
     top = chosen.shape[1]
-    experts, _, hidden, _ = w_gate_up.shape
+    experts, hidden = w_gate_up.shape[0], w_gate_up.shape[-2]
+    act_code = ACTIVATIONS[act] if act is not None else -1
     grouped = (x.dtype == torch.bfloat16 and MOE_GROUPED_MIN_PAIRS > 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                and x.data_ptr() % 16 == 0 and (shared is None or (shared.stride(1) == 1 and shared.stride(0) % 2 == 0)))
     if grouped and MOE_TC_MIN_PAIRS > 0 and n * top >= MOE_TC_MIN_PAIRS and d % 64 == 0 and hidden % 64 == 0:
@@ -1289,7 +1417,7 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_
         _check(lib.tis_moe_grouped_tc(_p(x), x.stride(0), _p(chosen), _p(weights), _p(w_gate_up), _p(w_down), _p(shared),
                                       shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), _p(sorted_pair),
                                       _p(pair_place), _p(tile_expert), _p(xs), _p(hid), _p(y), n, d, top, experts, hidden,
-                                      _p(tc_fault()), _stream()), lib)
+                                      act_code, _p(tc_fault()), _stream()), lib)
         return out
     if (grouped and n * top >= MOE_GROUPED_MIN_PAIRS and d % 32 == 0
             and hidden % 32 == 0):
@@ -1305,6 +1433,7 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_
         launches += 3
         _check(lib.tis_moe_grouped(_p(x), x.stride(0), _p(chosen), _p(weights), _p(w_gate_up), _p(w_down), _p(shared),
                                    shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), _p(sorted_pair),
-                                   _p(pair_place), _p(tile_expert), _p(hid), _p(y), n, d, top, experts, hidden, _stream()), lib)
+                                   _p(pair_place), _p(tile_expert), _p(hid), _p(y), n, d, top, experts, hidden, act_code,
+                                   _stream()), lib)
         return out
-    return moe_down(moe_gate_up(x, chosen, w_gate_up), chosen, weights, w_down, shared, shared_gate)
+    return moe_down(moe_gate_up(x, chosen, w_gate_up, act), chosen, weights, w_down, shared, shared_gate)

@@ -6,7 +6,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, Part, WeightSpec
+from .base import BuildContext, Part, StateSpec, WeightSpec
 
 
 class Embedding(Part):
@@ -31,6 +31,40 @@ class Embedding(Part):
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         out = torch.empty((tokens.shape[0], self.width), dtype=torch.float32, device=tokens.device)
         return ops.embed_rows(self.table, tokens, out, self.scale)
+
+
+class PairHashEmbedding(Embedding):
+    """``x = E[token] * scale + P[(previous * mul_prev + token * mul_cur) mod buckets]``: beside the token's own row a row
+    of a second table ``P (buckets + 1, width)`` addressed by a hash of the token and the one before it; the first token
+    of a sequence has no predecessor and takes the table's last row.  The previous token of a request is per-request
+    state (``state_spec``: one int32), which ``forward`` reads for the first row a request has in the step and brings up
+    to date."""
+
+    def __init__(self, vocab: int, width: int, buckets: int, mul_prev: int, mul_cur: int, prefix: str = "",
+                 weight_name: str = "embedding.weight", pairs_name: str = "bigram", scale: float = 1.0):
+        super().__init__(vocab, width, prefix=prefix, weight_name=weight_name, scale=scale)
+        if buckets <= 0:
+            raise ValueError(f"a hashed table of {buckets} buckets")
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pairs_name = pairs_name
+        self.pairs: Optional[torch.Tensor] = None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((1,), torch.int32)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        specs[self.pairs_name] = WeightSpec((self.buckets + 1, self.width))
+        return specs
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        super().load(tensors, ctx)
+        self.pairs = tensors[self.prefix + self.pairs_name].to(device=ctx.device, dtype=ctx.dtype).contiguous()
+
+    def forward(self, tokens: torch.Tensor, step=None, state: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = torch.empty((tokens.shape[0], self.width), dtype=torch.float32, device=tokens.device)
+        return ops.embed_pairs(self.table, self.pairs, tokens, step.positions, step.row_slot, step.row_last, state, out,
+                               self.scale, self.buckets, self.mul_prev, self.mul_cur)
 
 
 class LMHead(Part):

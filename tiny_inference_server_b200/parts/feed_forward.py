@@ -150,6 +150,10 @@ class RoutedExperts(FeedForward):
     * ``shared_hidden`` > 0: one more unit of that hidden size runs for every token and is added times
       ``sigmoid(w_sg . h)``, one number per token.
 
+    Options: ``scores`` ``"softmax_chosen"``: the logits ``z`` themselves choose (the ``top`` largest) and the weights are
+    the softmax over the chosen logits only; ``correction`` False: there is no correction tensor; ``unit_act`` (a name of
+    ``kernels.ops.ACTIVATIONS``): the experts have no gate, ``W_down act(W_up h)``, and no ``e<i>.gate`` tensors.
+
     Tensor names below the prefix: ``e<i>.gate, e<i>.up, e<i>.down``, ``router``, ``correction``, ``shared.gate,
     shared.up, shared.down, shared.sg`` (matrices stored (out, in)).  On the device the experts' matrices are stacked:
     gate and up ``(experts, 2, hidden, width)``, down ``(experts, width, hidden)``; the kernels find an expert's rows
@@ -158,8 +162,14 @@ class RoutedExperts(FeedForward):
     WEIGHT_EPS = 1e-20
 
     def __init__(self, width: int, hidden: int, experts: int, top: int, groups: int = 0, keep: int = 0,
-                 shared_hidden: int = 0, prefix: str = ""):
+                 shared_hidden: int = 0, prefix: str = "", scores: str = "sigmoid", correction: bool = True,
+                 unit_act: Optional[str] = None):
         super().__init__(prefix)
+        if scores not in ops.ROUTER_SCORES:
+            raise ValueError(f"router scores {scores!r}: known are {sorted(ops.ROUTER_SCORES)}")
+        if unit_act is not None and unit_act not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {unit_act!r}: known are {sorted(ops.ACTIVATIONS)}")
+        self.scores, self.has_correction, self.unit_act = scores, correction, unit_act
         if groups and (experts % groups or not (0 < keep <= groups)):
             raise ValueError(f"{experts} experts in {groups} groups, {keep} kept")
         if top > (experts // groups * keep if groups else experts):
@@ -171,21 +181,24 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = self.w_down = self.w_router = self.correction = self.w_shared_gate = None
 
     @classmethod
-    def from_config(cls, cfg, prefix: str, layer_index: int):
+    def from_config(cls, cfg, prefix: str, layer_index: int, **options):
         f = cfg.layers[layer_index]["mlp"]
         r = f["router"]
         g = r.get("groups") or {}
         s = f.get("shared") or {}
         return cls(cfg.hidden_size, f["expert"]["ff"], r["experts"], r["top"], g.get("count", 0), g.get("keep", 0),
-                   s.get("ff", 0), prefix=prefix)
+                   s.get("ff", 0), prefix=prefix, **options)
 
     def children(self):
         return (self.shared,) if self.shared is not None else ()
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        specs = {"router": WeightSpec((self.experts, self.width)), "correction": WeightSpec((self.experts,))}
+        specs = {"router": WeightSpec((self.experts, self.width))}
+        if self.has_correction:
+            specs["correction"] = WeightSpec((self.experts,))
         for e in range(self.experts):
-            specs[f"e{e}.gate"] = WeightSpec((self.hidden, self.width))
+            if self.unit_act is None:
+                specs[f"e{e}.gate"] = WeightSpec((self.hidden, self.width))
             specs[f"e{e}.up"] = WeightSpec((self.hidden, self.width))
             specs[f"e{e}.down"] = WeightSpec((self.width, self.hidden))
         if self.shared is not None:
@@ -196,19 +209,22 @@ class RoutedExperts(FeedForward):
         p = self.prefix
         dev = dict(device=ctx.device, dtype=ctx.dtype)
         f32 = dict(device=ctx.device, dtype=torch.float32)
-        gu = torch.stack([torch.stack([tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"]]) for e in range(self.experts)])
+        if self.unit_act is None:
+            gu = torch.stack([torch.stack([tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"]]) for e in range(self.experts)])
+        else:                                   # units without a gate: (experts, hidden, width)
+            gu = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.experts)])
         self.w_gate_up = gu.to(**dev).contiguous()
         self.w_down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.experts)]).to(**dev).contiguous()
         self.w_router = tensors[p + "router"].to(**f32).contiguous()
-        self.correction = tensors[p + "correction"].to(**f32).contiguous()
+        self.correction = tensors[p + "correction"].to(**f32).contiguous() if self.has_correction else None
         if self.shared is not None:
             self.w_shared_gate = tensors[p + "shared.sg"].to(**f32).reshape(-1).contiguous()
 
     def forward(self, x, step=None):
         chosen, weights, shared_gate = ops.moe_route(x, self.w_router, self.correction, self.w_shared_gate, self.groups,
-                                                     self.keep, self.top, self.WEIGHT_EPS)
+                                                     self.keep, self.top, self.WEIGHT_EPS, scores=self.scores)
         shared = self.shared.forward(x, step) if self.shared is not None else None
-        return ops.moe_experts(x, chosen, weights, self.w_gate_up, self.w_down, shared, shared_gate)
+        return ops.moe_experts(x, chosen, weights, self.w_gate_up, self.w_down, shared, shared_gate, act=self.unit_act)
 
 
 register_part("ffn", "swiglu", SwiGLU)
