@@ -148,7 +148,7 @@ def _segments(row_slot):
     return segs
 
 
-def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=False):
+def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=False, bias=None):
     taps, c = weight.shape
     hist = taps - 1
     for r0, rows, slot in _segments(row_slot):
@@ -158,6 +158,8 @@ def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=
         y = torch.zeros((rows, c), dtype=torch.float32)
         for j in range(taps):
             y += weight[j] * seq[j:j + rows]
+        if bias is not None:
+            y += bias
         if residual:
             y += seq[hist:]
         if silu:
@@ -371,9 +373,9 @@ def gemm_heads(a, w, out):
     return out
 
 
-def moe_route(x, w_router, correction, w_shared_gate, groups, keep, top, weight_eps=1e-20):
+def moe_route(x, w_router, correction, w_shared_gate, groups, keep, top, weight_eps=1e-20, scores="sigmoid"):
     xf = x.to(torch.float32)
-    s = torch.sigmoid(xf @ w_router.t())
+    s = xf @ w_router.t() if scores == "softmax_chosen" else torch.sigmoid(xf @ w_router.t())
     n, experts = s.shape
     pick = s + correction if correction is not None else s.clone()
     if groups:
@@ -384,22 +386,144 @@ def moe_route(x, w_router, correction, w_shared_gate, groups, keep, top, weight_
         pick = per.masked_fill(~ok[:, :, None], float("-inf")).reshape(n, experts)
     chosen = pick.topk(top, dim=-1).indices
     w = s.gather(1, chosen)
-    w = w / (w.sum(-1, keepdim=True) + weight_eps)
+    w = torch.softmax(w, dim=-1) if scores == "softmax_chosen" else w / (w.sum(-1, keepdim=True) + weight_eps)
     shared = torch.sigmoid(xf @ w_shared_gate) if w_shared_gate is not None else None
     return chosen.to(torch.int32), w, shared
 
 
-def moe_gate_up(x, chosen, w_gate_up):
+def _act(z, kind):
+    if kind == "relu2":
+        return torch.clamp(z, min=0.0) ** 2
+    if kind == "gelu_tanh":
+        return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    return z * torch.sigmoid(z)
+
+
+def moe_gate_up(x, chosen, w_gate_up, act=None):
     n, top = chosen.shape
     xf = x.to(torch.float32)
+    if act is not None:
+        u = torch.einsum("ntfd,nd->ntf", w_gate_up.to(torch.float32)[chosen.long()], xf)
+        return _act(u, act).reshape(n * top, -1).to(x.dtype)
     w = w_gate_up.to(torch.float32)[chosen.long()]                      # (n, top, 2, F, d)
     g = torch.einsum("ntfd,nd->ntf", w[:, :, 0], xf)
     u = torch.einsum("ntfd,nd->ntf", w[:, :, 1], xf)
     return (g * torch.sigmoid(g) * u).reshape(n * top, -1).to(x.dtype)
 
 
-def moe_experts(x, chosen, weights, w_gate_up, w_down, shared, shared_gate):
-    return moe_down(moe_gate_up(x, chosen, w_gate_up), chosen, weights, w_down, shared, shared_gate)
+def moe_experts(x, chosen, weights, w_gate_up, w_down, shared, shared_gate, act=None):
+    return moe_down(moe_gate_up(x, chosen, w_gate_up, act), chosen, weights, w_down, shared, shared_gate)
+
+
+def gated_linear_attention(qkv, a_in, power, a_bias, gate, norm_weight, eps, q_scale, state, out, row_slot, row_last,
+                           num_heads, k_dim, v_dim, requests=None, segments=None, gate_act="silu"):
+    H = num_heads
+    nq = H * k_dim
+    for r0, rows, slot in _segments(row_slot):
+        S = state[slot, :H * k_dim * v_dim].reshape(H, k_dim, v_dim).to(torch.float32).clone()
+        for r in range(r0, r0 + rows):
+            row = qkv[r].to(torch.float32)
+            q = row[:nq].view(H, k_dim) * q_scale
+            k = row[nq:2 * nq].view(H, k_dim)
+            v = row[2 * nq:2 * nq + H * v_dim].view(H, v_dim)
+            z = a_in[r].to(torch.float32).view(H, k_dim) + a_bias.view(H, k_dim)
+            alpha = torch.exp(torch.nn.functional.logsigmoid(z) * power.view(H, 1))
+            S = alpha[:, :, None] * S + k[:, :, None] * v[:, None, :]
+            o = torch.einsum("hdv,hd->hv", S, q)
+            o = (o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_weight).reshape(-1)
+            if gate is not None:
+                g = gate[r].to(torch.float32)
+                o = o * (g * torch.sigmoid(g) if gate_act == "silu" else torch.sigmoid(g))
+            out[r] = o.to(out.dtype)
+        state[slot, :H * k_dim * v_dim] = S.reshape(-1)
+    return out
+
+
+def state_space_scan(cbx, dt_in, a_log, dt_bias, state, row_slot, row_last, num_heads, groups, state_dim, v_dim,
+                     requests=None, segments=None):
+    H, G, N = num_heads, groups, state_dim
+    raw = torch.zeros((cbx.shape[0], H * v_dim), dtype=torch.float32)
+    head_group = torch.arange(H) // (H // G)
+    for r0, rows, slot in _segments(row_slot):
+        S = state[slot, :H * N * v_dim].reshape(H, N, v_dim).to(torch.float32).clone()
+        for r in range(r0, r0 + rows):
+            row = cbx[r].to(torch.float32)
+            C = row[:G * N].view(G, N)[head_group]
+            B = row[G * N:2 * G * N].view(G, N)[head_group]
+            x = row[2 * G * N:2 * G * N + H * v_dim].view(H, v_dim)
+            dt = torch.nn.functional.softplus(dt_in[r].to(torch.float32)[:H] + dt_bias)
+            S = torch.exp(-torch.exp(a_log) * dt)[:, None, None] * S + B[:, :, None] * (dt[:, None] * x)[:, None, :]
+            raw[r] = torch.einsum("hnv,hn->hv", S, C).reshape(-1)
+        state[slot, :H * N * v_dim] = S.reshape(-1)
+    return raw
+
+
+def skip_gate_group_norm(o_raw, x, skip, z, weight, groups, eps, out, row_slot, num_heads, v_dim):
+    n, d = o_raw.shape
+    zf = z.to(torch.float32)
+    y = (o_raw + skip.repeat_interleave(v_dim)[None, :] * x.to(torch.float32)) * (zf * torch.sigmoid(zf))
+    parts = y.view(n, groups, d // groups)
+    y = (parts / torch.sqrt(parts.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, d) * weight
+    out[:] = y.to(out.dtype)
+    return out
+
+
+def embed_pairs(table, pairs, tokens, positions, row_slot, row_last, prev, out, scale, buckets, mul_prev, mul_cur):
+    toks = [int(t) for t in tokens]
+    for r0, rows, slot in _segments(row_slot):
+        for r in range(r0, r0 + rows):
+            before = toks[r - 1] if r > r0 else (int(prev[slot, 0]) if int(positions[r]) > 0 else None)
+            which = buckets if before is None else (before * mul_prev + toks[r] * mul_cur) % buckets
+            out[r] = table[toks[r]].to(torch.float32) * scale + pairs[which].to(torch.float32)
+        prev[slot, 0] = toks[r0 + rows - 1]
+    return out
+
+
+def group_norm(residual, delta_a, delta_b, groups, eps, w1, out1, w2=None, out2=None, in_place=False, dtype=None):
+    for d in (delta_a, delta_b):
+        if d is not None:
+            residual += d.to(torch.float32)
+    if w1 is None:
+        return out1, out2
+    n, width = residual.shape
+    parts = residual.view(n, groups, width // groups)
+    normed = (parts / torch.sqrt(parts.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, width)
+    if in_place:
+        residual.copy_(normed * w1)
+    elif out1 is not None:
+        out1[:] = (normed * w1).to(out1.dtype)
+    if out2 is not None:
+        out2[:] = (normed * w2).to(out2.dtype)
+    return out1, out2
+
+
+def rotate_tie_store(qk, num_heads, kv_heads, dim, rot, cos, sin, k_pages, v_pages, block_table, positions, row_slot,
+                     page_size, fault):
+    half = rot // 2
+
+    def turn(z, pos):                   # (heads, dim)
+        if not rot:
+            return z
+        c, s = cos[pos], sin[pos]
+        a, b = z[:, :half], z[:, half:rot]
+        return torch.cat([a * c - b * s, b * c + a * s, z[:, rot:]], dim=-1)
+
+    for r in range(qk.shape[0]):
+        slot = int(row_slot[r])
+        if slot < 0:
+            continue
+        pos = int(positions[r])
+        row = qk[r].to(torch.float32)
+        q = row[:num_heads * dim].view(num_heads, dim)
+        k = row[num_heads * dim:(num_heads + kv_heads) * dim].view(kv_heads, dim)
+        qk[r, :num_heads * dim] = turn(q, pos).reshape(-1).to(qk.dtype)
+        page = int(block_table[slot, pos // page_size])
+        k_pages[page, :, pos % page_size, :] = turn(k, pos).to(k_pages.dtype)
+        v_pages[page, :, pos % page_size, :] = k.to(v_pages.dtype)
+
+
+def scaled_sum(a, scale_a, b, scale_b):
+    return (a.to(torch.float32) * scale_a + b.to(torch.float32) * scale_b).to(a.dtype)
 
 
 def moe_down(hidden, chosen, weights, w_down, shared, shared_gate):
@@ -656,7 +780,8 @@ _NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set", "glu_clamped", "scale_f32", "causal_conv",
           "softcap_f32", "activation", "gemm_act", "forget_gate_recurrence", "head_norm_store", "diff_combine",
           "norm_mix_store", "window_attention", "delta_rule", "linear_attention", "latent_prepare", "gemm_heads", "moe_route",
-          "moe_gate_up", "moe_down", "moe_experts"]
+          "moe_gate_up", "moe_down", "moe_experts", "gated_linear_attention", "state_space_scan", "skip_gate_group_norm",
+          "embed_pairs", "group_norm", "rotate_tie_store", "scaled_sum"]
 
 
 def install(monkeypatch) -> None:

@@ -1,0 +1,913 @@
+"""The Kubolorn architecture through the engine against the plain implementation (``plain_kubolorn``): configuration and
+weights, every mechanism alone with planted inputs, replays cut in every way, configurations drawn at random, slots used
+again, long decoding, generation through the scheduler and the command line."""
+from __future__ import annotations
+
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kubolorn as plain
+import trace_tools
+from tiny_inference_server_b200 import ConfigError, build_model, config_from_dict, config_from_folder
+from tiny_inference_server_b200.api import Engine, SamplingParams
+from tiny_inference_server_b200.config import EngineConfig, KubolornConfig
+from tiny_inference_server_b200.trace import TraceReplayer, make_runner
+from tiny_inference_server_b200.weights.loader import WeightError
+
+gpu = pytest.mark.gpu
+
+
+def _gla(heads, dim, vdim, tau=8.0):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}
+
+
+def _par(heads, kv, dim, rot_dims, s_heads, s_vdim, state, groups, norm_groups, conv, base=10000.0, scaling=None, scale=None,
+         left_scale=0.8, right_scale=1.3):
+    rot = {"base": base, "dims": rot_dims}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "rot": rot,
+                     "scale": scale if scale is not None else dim ** -0.5},
+            "right": {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": groups, "norm_groups": norm_groups, "conv": conv},
+            "left_scale": left_scale, "right_scale": right_scale}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def _moe(ff, experts, top):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def _cfg(vocab, width, layers, groups=1, taps=3, buckets=61, muls=(31, 7), scale=3.0, loop=None, eps=1e-5):
+    c = dict(architecture="Kubolorn", vocab=vocab, width=width, norm={"eps": eps, "groups": groups},
+             embedding={"scale": scale, "bigram": {"buckets": buckets, "mul_prev": muls[0], "mul_cur": muls[1]}},
+             canon={"taps": taps}, layers=layers)
+    if loop:
+        c["loop"] = dict(zip(("start", "stop", "times"), loop))
+    return c
+
+
+# a looped span of two kinds of layer; kv heads below the query heads; a rotation over half of every head with rescaling
+K1 = _cfg(97, 64, [
+    {"type": "gla", "mixer": _gla(2, 16, 32), "mlp": _dense(96)},
+    {"type": "parallel", "mixer": _par(4, 2, 32, 16, 4, 16, 16, 2, 4, 3, scaling=(4.0, 64, 8.0, 1.0)), "mlp": _moe(32, 8, 2)},
+    {"type": "gla", "mixer": _gla(4, 16, 16, tau=3.0), "mlp": _moe(32, 8, 3)},
+], groups=4, taps=3, loop=(1, 3, 2))
+# sizes that fit no vector or tile; no loop; a layer without a feed-forward; every query head with keys of its own; the
+# whole head rotated, no rescaling; one expert a token; taps of two
+K2 = _cfg(53, 40, [
+    {"type": "parallel", "mixer": _par(2, 2, 10, 10, 3, 10, 12, 1, 1, 2, scale=0.4, left_scale=1.0, right_scale=1.0),
+     "mlp": _moe(24, 5, 1)},
+    {"type": "gla", "mixer": _gla(3, 10, 6, tau=1.0), "mlp": None},
+    {"type": "gla", "mixer": _gla(1, 24, 40, tau=20.0), "mlp": _dense(50)},
+], groups=1, taps=2, buckets=1, muls=(3, 5), scale=1.0)
+# widths that the tensor-core attention and the split recurrence kernels take; the attention layer inside the loop (a cache
+# plane per pass); every expert chosen
+K3 = _cfg(200, 128, [
+    {"type": "gla", "mixer": _gla(4, 64, 64, tau=16.0), "mlp": _moe(64, 4, 4)},
+    {"type": "parallel", "mixer": _par(8, 1, 64, 32, 4, 64, 64, 2, 2, 4, base=500.0, scaling=(2.0, 32, 4.0, 0.5)),
+     "mlp": _dense(256)},
+    {"type": "gla", "mixer": _gla(2, 32, 64, tau=4.0), "mlp": _dense(64)},
+], groups=2, taps=4, buckets=509, muls=(127, 17), scale=11.3, loop=(0, 2, 3))
+# a convolution of one tap (no history at all) in front of the sublayers; a loop that runs once; groups of one element's
+# worth of heads; two parallel layers with different sizes (two cache groups)
+K4 = _cfg(64, 48, [
+    {"type": "parallel", "mixer": _par(3, 1, 16, 8, 2, 24, 8, 2, 1, 4, left_scale=1.5, right_scale=0.5), "mlp": _dense(64)},
+    {"type": "gla", "mixer": _gla(2, 8, 24, tau=2.0), "mlp": _moe(16, 6, 2)},
+    {"type": "parallel", "mixer": _par(2, 2, 24, 24, 6, 8, 16, 3, 3, 3, scaling=(8.0, 16, 2.0, 1.0)), "mlp": None},
+], groups=3, taps=1, buckets=7, muls=(0, 1), scale=0.5, loop=(1, 2, 1))
+
+CONFIGS = {"K1": (K1, 16), "K2": (K2, 8), "K3": (K3, 16), "K4": (K4, 4)}
+LENGTHS = {"K1": [1, 2, 3, 30, 75, 41, 9, 60], "K2": [1, 5, 40, 33, 17, 64], "K3": [2, 4, 50, 140, 23, 37],
+           "K4": [1, 2, 2, 19, 33, 6, 80]}
+
+
+def make_tensors(cfg, seed):
+    """Weights of a size that makes every mechanism matter, rounded to bfloat16 so that both precisions and the plain
+    implementation hold the same numbers: decays from nearly nothing to nearly one, step sizes over two orders of
+    magnitude, routers whose logits lie apart."""
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, spec in build_model(cfg).expected_tensors().items():
+        shape = tuple(spec.shape)
+        leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
+        rnd = torch.randn(shape, generator=gen)
+        uni = torch.rand(shape, generator=gen)
+        if name == "embed":
+            t = rnd
+        elif name == "bigram":
+            t = rnd * 0.7
+        elif leaf.endswith("norm") or leaf in ("norm1", "norm2"):
+            t = 1.0 + rnd * 0.2
+        elif leaf in ("canon1", "canon2"):
+            t = rnd * 0.4
+        elif leaf == "mix.right.conv":
+            t = rnd * 0.5
+        elif leaf == "mix.right.conv.b":
+            t = rnd * 0.3
+        elif leaf == "mix.a2.b":
+            t = uni * 7.0 - 1.0
+        elif leaf == "mix.left.sink":
+            t = rnd
+        elif leaf == "mix.right.dt_bias":
+            t = uni * 4.0 - 3.5
+        elif leaf == "mix.right.A_log":
+            t = uni * 3.0 - 2.5
+        elif leaf == "mix.right.D":
+            t = 1.0 + rnd * 0.3
+        elif len(shape) == 2:
+            gain = {"mix.q": 2.0, "mix.k": 2.0, "mix.left.q": 2.0, "mix.left.k": 2.0, "mlp.router": 4.0}.get(leaf, 1.0)
+            t = rnd * gain / math.sqrt(shape[1])
+        else:
+            raise AssertionError(f"no rule for {name} {shape}")
+        out[name] = t.to(torch.bfloat16).contiguous()
+    return out
+
+
+def make_folder(raw, seed, folder):
+    from safetensors.torch import save_file
+    cfg = config_from_dict(json.loads(json.dumps(raw)))
+    for i, layer in enumerate(cfg.layers):                 # the rank of the gates' projection lives in the shapes only
+        if layer["type"] == "gla":
+            layer["mixer"]["decay_rank"] = 4 + 3 * i
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(raw, f)
+    save_file(make_tensors(cfg, seed), os.path.join(folder, "model.safetensors"))
+    return folder
+
+
+def read_folder(folder):
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as f:
+        c = json.load(f)
+    W = {k: v.to(torch.float64) for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    return c, W
+
+
+_cache = {}
+
+
+def _setup(name, tmp_path_factory):
+    if name not in _cache:
+        raw, page = CONFIGS[name]
+        folder = make_folder(raw, 23 + ord(name[-1]), str(tmp_path_factory.mktemp(f"kubolorn{name}")))
+        c, W = read_folder(folder)
+        g = torch.Generator().manual_seed(5)
+        seqs = {f"r{i}": torch.randint(0, raw["vocab"], (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[name])}
+        ref = {rid: plain.plain_forward(c, W, toks).numpy() for rid, toks in seqs.items()}
+        _cache[name] = (raw, page, folder, seqs, ref, c, W)
+    return _cache[name]
+
+
+def rel_err(got, ref):
+    """Difference of two rows of logits, mean taken off, root mean square, over that of the reference."""
+    d = np.asarray(got, dtype=np.float64) - ref
+    d = d - d.mean()
+    r = ref - ref.mean()
+    return float(np.sqrt((d * d).mean()) / max(np.sqrt((r * r).mean()), 1e-9))
+
+
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+#: In float32 every position agrees.  In bfloat16 a few positions in a hundred may differ by more than the tolerance (by
+#: less than 1): a router whose two best logits lie within a rounding of each other picks another expert there.
+BF16_OUTLIERS = {"float32": 0.0, "bfloat16": 0.03}
+
+
+def _steps(mode, seqs, max_live=4):
+    if mode == "whole":
+        return trace_tools.trace_whole(seqs)
+    if mode == "tail":
+        return trace_tools.trace_tail(seqs, tail=32)
+    if mode == "chunks":
+        return trace_tools.trace_chunks(seqs)
+    return trace_tools.trace_mixed(seqs, max_live=max_live)
+
+
+def _replay_and_compare(raw, page, folder, seqs, ref, steps, out_dir, dtype, device, tol, max_live=4, poison=False,
+                        shuffle=False, outliers=0.0):
+    """``outliers``: the share of positions that may exceed the tolerance (none of them by more than 1)."""
+    runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, device=device,
+                         max_live=max_live, debug_poison=poison)
+    if shuffle:
+        import random
+        for g in runner.cache.groups:
+            g.pool.shuffle(random.Random(3))
+    TraceReplayer(runner, out_dir).run(json.dumps(s) for s in steps)
+    runner.cache.check()
+    assert runner.cache.drained(), "pages or slots were not given back"
+    got = trace_tools.gather(steps, out_dir, raw["vocab"])
+    worst, over, total = 0.0, [], sum(len(t) for t in seqs.values())
+    for rid, toks in seqs.items():
+        for p in range(len(toks)):
+            e = rel_err(got[rid][p], ref[rid][p])
+            if e >= tol:
+                over.append((rid, p, e))
+                assert e < 1.0 and len(over) <= outliers * total, \
+                    f"logits of {rid} at position {p}: relative error {e} (first wrong place; over the tolerance so far: {over})"
+            worst = max(worst, e)
+    return runner, worst
+
+
+# ------------------------------------------------------------------------------------------------
+# configuration and weights (CPU)
+# ------------------------------------------------------------------------------------------------
+
+def test_config_round_trip_and_tensor_names(tmp_path):
+    folder = make_folder(K1, 1, str(tmp_path / "m"))
+    cfg = config_from_folder(folder)
+    assert isinstance(cfg, KubolornConfig) and cfg.norm_groups == 4 and cfg.canon_taps == 3
+    assert cfg.layers[0]["mixer"]["decay_rank"] == 4 and cfg.layers[2]["mixer"]["decay_rank"] == 10      # from the shapes
+    assert cfg.layer_runs() == [0, 1, 2, 1, 2]
+    again = config_from_dict(cfg.to_dict())
+    assert again.to_dict() == cfg.to_dict()
+    model = build_model(cfg)
+    names = set(model.expected_tensors())
+    assert {"embed", "bigram", "embed.norm", "final.norm", "l0.canon1", "l0.canon2", "l0.mix.a2.b", "l1.mix.left.sink",
+            "l1.mix.right.conv.b", "l1.mix.right.A_log", "l1.mlp.e7.up", "l1.mlp.router", "l2.mlp.e0.down"} <= names
+    assert not any(n.endswith(".gate") or n.endswith("correction") or n.endswith("left.v") for n in names)
+    # a layer of the looped span runs twice: one block, two entries, a state and a cache plane each
+    assert len(model.entries) == 5 and model.entries[1].block is model.entries[3].block
+    assert sum(s is not None for s in model.kv_specs()) == 2
+    k4 = build_model(config_from_folder(make_folder(K4, 1, str(tmp_path / "k4"))))
+    assert len({s.group_key() for s in k4.kv_specs() if s is not None}) == 2
+
+
+def test_config_errors_name_the_problem():
+    def broken(change):
+        raw = json.loads(json.dumps(K1))
+        change(raw)
+        with pytest.raises(ConfigError) as e:
+            config_from_dict(raw)
+        return str(e.value)
+
+    assert "norm.groups" in broken(lambda r: r["norm"].update(groups=5))
+    assert "loop" in broken(lambda r: r["loop"].update(stop=9))
+    assert "layers[0].type" in broken(lambda r: r["layers"][0].update(type="attention"))
+    assert "tau" in broken(lambda r: r["layers"][0]["mixer"].update(tau=0))
+    assert "kv heads" in broken(lambda r: r["layers"][1]["mixer"]["left"].update(kv_heads=3))
+    assert "vdim must equal dim" in broken(lambda r: r["layers"][1]["mixer"]["left"].update(vdim=8))
+    assert "rot.dims" in broken(lambda r: r["layers"][1]["mixer"]["left"]["rot"].update(dims=34))
+    assert "groups" in broken(lambda r: r["layers"][1]["mixer"]["right"].update(groups=3))
+    assert "norm_groups" in broken(lambda r: r["layers"][1]["mixer"]["right"].update(norm_groups=5))
+    assert "top" in broken(lambda r: r["layers"][1]["mlp"]["router"].update(top=9))
+    assert "bigram" in broken(lambda r: r["embedding"]["bigram"].update(buckets=0))
+    assert "canon.taps" in broken(lambda r: r["canon"].update(taps=40))
+
+
+def test_a_missing_or_misshapen_tensor_is_named(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from tiny_inference_server_b200.weights.loader import load_weights
+    folder = make_folder(K2, 2, str(tmp_path / "m"))
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    del tensors["l0.mix.left.sink"]
+    tensors["l0.mix.right.conv.b"] = tensors["l0.mix.right.conv.b"][:-1].contiguous()
+    tensors["l0.mix.left.v"] = torch.zeros(4, 4)
+    save_file(tensors, path)
+    model = build_model(config_from_folder(folder))
+    with pytest.raises(WeightError) as e:
+        load_weights(folder, model.expected_tensors())
+    msg = str(e.value)
+    assert "l0.mix.left.sink" in msg and "l0.mix.right.conv.b" in msg and "l0.mix.left.v" in msg
+    os.remove(path)
+    tensors.pop("l1.mix.a1")
+    save_file(tensors, path)
+    with pytest.raises(ConfigError) as e:
+        config_from_folder(folder)
+    assert "l1.mix.a1" in str(e.value)
+
+
+# ------------------------------------------------------------------------------------------------
+# the plain implementation against other ways of writing the same sums (CPU)
+# ------------------------------------------------------------------------------------------------
+
+def _selectors(width, parts):
+    """Projections that pick columns: ``parts`` = [(name, columns)], side by side from column 0.  With them a plain
+    mixer reads its queries, keys and values straight out of its input, so that a test can plant them."""
+    W, at = {}, 0
+    for name, n in parts:
+        W[name] = torch.zeros(n, width, dtype=torch.float64)
+        W[name][torch.arange(n), at + torch.arange(n)] = 1.0
+        at += n
+    return W
+
+
+def test_plain_recurrences_as_explicit_sums():
+    """Gated linear attention and the state space written as sums over all earlier tokens instead of a state."""
+    g = torch.Generator().manual_seed(3)
+    L, H, D, V, R = 9, 2, 4, 3, 2
+    m = _gla(H, D, V, tau=3.0)
+    width = 2 * H * D + 2 * H * V + R
+    W = _selectors(width, [("q", H * D), ("k", H * D), ("v", H * V), ("g", H * V), ("a1", R)])
+    W.update({"a2": torch.randn(H * D, R, generator=g, dtype=torch.float64), "a2.b": torch.randn(H * D, generator=g, dtype=torch.float64),
+              "norm": torch.ones(V, dtype=torch.float64), "o": torch.eye(H * V, dtype=torch.float64)})
+    u = torch.randn(L, width, generator=g, dtype=torch.float64)
+    got = plain.gated_linear_attention(u, W, "", m, 0.0)
+    q = u[:, :H * D].view(L, H, D) * D ** -0.5
+    k = u[:, H * D:2 * H * D].view(L, H, D)
+    v = u[:, 2 * H * D:2 * H * D + H * V].view(L, H, V)
+    gate = u[:, 2 * H * D + H * V:2 * H * D + 2 * H * V]
+    z = u[:, -R:] @ W["a2"].T + W["a2.b"]
+    log_alpha = (torch.log(torch.sigmoid(z)) / 3.0).view(L, H, D)
+    want = torch.zeros(L, H, V, dtype=torch.float64)
+    for t in range(L):
+        for j in range(t + 1):
+            carried = torch.exp(log_alpha[j + 1:t + 1].sum(0))          # (H, D): the decays between j and t
+            want[t] += ((q[t] * carried * k[j]).sum(-1))[:, None] * v[j]
+    want = want / torch.sqrt((want * want).mean(-1, keepdim=True))
+    want = want.reshape(L, H * V) * (gate * torch.sigmoid(gate))
+    assert float((got - want).abs().max()) < 1e-9
+
+    Hs, P, N, G = 4, 3, 5, 2
+    m = {"heads": Hs, "vdim": P, "state": N, "groups": G, "norm_groups": 1, "conv": 1}
+    inner = Hs * P
+    width = 2 * inner + 2 * G * N + Hs
+    W = {"in": torch.eye(width, dtype=torch.float64), "conv": torch.ones(inner + 2 * G * N, 1, dtype=torch.float64),
+         "conv.b": torch.zeros(inner + 2 * G * N, dtype=torch.float64), "dt_bias": torch.randn(Hs, generator=g, dtype=torch.float64),
+         "A_log": torch.randn(Hs, generator=g, dtype=torch.float64), "D": torch.randn(Hs, generator=g, dtype=torch.float64),
+         "norm": torch.ones(inner, dtype=torch.float64), "o": torch.eye(inner, dtype=torch.float64)}
+    u = torch.randn(L, width, generator=g, dtype=torch.float64)
+    got = plain.state_space_duality(u, W, "", m, 0.0)
+    zz = u[:, :inner]
+    xbc = plain.silu(u[:, inner:2 * inner + 2 * G * N])
+    x, B, C = xbc[:, :inner].view(L, Hs, P), xbc[:, inner:inner + G * N].view(L, G, N), xbc[:, inner + G * N:].view(L, G, N)
+    dt = torch.log1p(torch.exp(u[:, -Hs:] + W["dt_bias"]))
+    a = -torch.exp(W["A_log"]) * dt                                       # log decay (L, Hs)
+    want = torch.zeros(L, Hs, P, dtype=torch.float64)
+    for h in range(Hs):
+        grp = h // (Hs // G)
+        for t in range(L):
+            for j in range(t + 1):
+                want[t, h] += torch.exp(a[j + 1:t + 1, h].sum()) * (C[t, grp] @ B[j, grp]) * dt[j, h] * x[j, h]
+            want[t, h] += W["D"][h] * x[t, h]
+    want = want.reshape(L, inner) * plain.silu(zz)
+    want = want / torch.sqrt((want * want).mean(-1, keepdim=True))
+    assert float((got - want).abs().max()) < 1e-9
+
+
+def test_plain_attention_sink_and_rotation():
+    """The keyless term takes probability away and gives nothing back; the rotation depends on the distance only, and the
+    values are not rotated."""
+    g = torch.Generator().manual_seed(4)
+    L, H, G, D = 7, 2, 1, 8
+    m = _par(H, G, D, 4, 1, 1, 1, 1, 1, 1, scaling=(4.0, 16, 4.0, 1.0))["left"]
+    W = _selectors(H * D + G * D, [("q", H * D), ("k", G * D)])
+    W["o"] = torch.eye(H * D, dtype=torch.float64)
+    u = torch.randn(L, H * D + G * D, generator=g, dtype=torch.float64)
+    W["sink"] = torch.tensor([-50.0, 50.0], dtype=torch.float64)
+    out = plain.sink_attention(u, W, "", m).view(L, H, D)
+    assert float(out[:, 1].abs().max()) < 1e-12                      # everything went to the sink
+    assert float((out[0, 0] - u[0, H * D:]).abs().max()) < 1e-12     # one key, no sink to speak of: the unrotated key itself
+    z = torch.randn(3, 1, D, generator=g, dtype=torch.float64)
+    a, b = plain.rotate(z, m["rot"], 5), plain.rotate(z, m["rot"], 11)
+    mag = 0.1 * math.log(4.0) + 1.0
+    assert abs(float((a[0] * a[1]).sum() - (b[0] * b[1]).sum())) < 1e-9
+    assert float((a[..., 4:] - z[..., 4:]).abs().max()) == 0.0
+    assert abs(float(a[0, 0, :4].norm() / z[0, 0, :4].norm()) - mag) < 1e-9
+
+
+# ------------------------------------------------------------------------------------------------
+# the engine's plumbing on the CPU, the kernels replaced by plain references
+# ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["K1", "K2", "K4"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+def test_replay_cpu(name, mode, tmp_path, tmp_path_factory, ref_ops):
+    raw, page, folder, seqs, ref, _, _ = _setup(name, tmp_path_factory)
+    seqs = {k: v for k, v in seqs.items() if len(v) <= 45}
+    _replay_and_compare(raw, page, folder, seqs, ref, _steps(mode, seqs, max_live=3), str(tmp_path / "out"), "float32", "cpu",
+                        TOL["float32"], max_live=3)
+
+
+def test_layers_of_the_stream_cpu(tmp_path_factory, ref_ops):
+    raw, page, folder, seqs, _, c, W = _setup("K1", tmp_path_factory)
+    _check_layers(folder, page, seqs["r3"], c, W, "cpu")
+
+
+def _check_layers(folder, page, toks, c, W, device):
+    from tiny_inference_server_b200.engine.batch import StepEntry
+    _, layers = plain.plain_forward(c, W, toks, return_layers=True)
+    runner = make_runner(folder, "float32", 128, page_size=page, max_live=1, cuda_graphs=False, device=device)
+    seen = []
+    spied = set()
+    for e in runner.model.entries:
+        if id(e.block) in spied:                  # a block of the looped span appears in several entries
+            continue
+        spied.add(id(e.block))
+        inner = e.block.forward
+
+        def spy(stream, step, binding, *a, _inner=inner, **kw):
+            _inner(stream, step, binding, *a, **kw)
+            seen.append(stream.flush().clone())
+        e.block.forward = spy
+    slot = runner.add_request()
+    runner.step([StepEntry(slot, list(toks), [len(toks) - 1])])
+    runner.release(slot)
+    assert len(seen) == len(plain.layer_runs(c)) == layers.shape[0]
+    for i, (got, want) in enumerate(zip(seen, layers)):
+        err = float((got.double().cpu() - want).abs().max() / want.abs().max())
+        assert err < 1e-4, f"stream after layer run {i}: {err}"
+
+
+def plain_greedy(c, W, prompt, new):
+    ids = list(prompt)
+    for _ in range(new):
+        ids.append(int(plain.plain_forward(c, W, ids)[-1].argmax()))
+    return ids[len(prompt):]
+
+
+def test_generate_cpu(tmp_path, tmp_path_factory, ref_ops):
+    raw, page, folder, seqs, _, c, W = _setup("K2", tmp_path_factory)
+    prompts = [seqs["r1"], seqs["r0"], seqs["r4"]]
+    want = [plain_greedy(c, W, p, 6) for p in prompts]
+    sp = SamplingParams(max_new_tokens=6, temperature=0.0, ignore_eos=True)
+    eng = Engine.from_folder(folder, EngineConfig(dtype="float32", page_size=page, num_pages=20, max_batch=2, device="cpu",
+                                                  max_tokens_per_step=7, cuda_graphs=False))
+    assert eng.generate(prompts, sp) == want
+    assert eng.runner.cache.drained()
+
+
+# ------------------------------------------------------------------------------------------------
+# every mechanism alone on the device, with planted inputs
+# ------------------------------------------------------------------------------------------------
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+MECH_TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def _close(got, ref, tol, what):
+    got = got.detach().double().cpu()
+    err = float((got - ref).abs().max() / max(float(ref.abs().max()), 1e-9))
+    assert err < tol, f"{what}: relative error {err}"
+
+
+def _rows(cuts, slots):
+    """row_slot and row_last of a step that holds ``cuts[i]`` rows of slot ``slots[i]``."""
+    row_slot, row_last = [], []
+    for n, s in zip(cuts, slots):
+        first = len(row_slot)
+        row_slot += [s] * n
+        row_last += [first + n - 1] * n
+    i32 = dict(dtype=torch.int32, device="cuda")
+    return torch.tensor(row_slot, **i32), torch.tensor(row_last, **i32)
+
+
+class _Step:
+    """What an attention kernel asks of a step, for one request's portion outside the engine."""
+
+    def __init__(self, positions, row_slot, decode_only=False):
+        self.positions, self.row_slot, self.decode_only = positions, row_slot, decode_only
+        self.max_position = int(positions.max())
+
+    def plan(self, planner):
+        return planner.infer(self.positions, self.row_slot)
+
+
+def _portions(L, cuts, alone=4):
+    """(index, first row, rows) of portions that follow ``cuts`` in turn; the last ``alone`` rows come one by one."""
+    fed, i = 0, 0
+    while fed < L:
+        n = min(cuts[i % len(cuts)], max(1, L - alone - fed)) if fed < L - alone else 1
+        yield i, fed, n
+        i += 1
+        fed += n
+
+
+def _round(t, dtype):
+    return t.to(DT[dtype]).to(torch.float64)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,kd,vd", [(2, 16, 24), (1, 16, 16), (3, 10, 6), (2, 64, 64), (1, 128, 32), (4, 48, 64), (2, 32, 128),
+                                     (1, 96, 320)])
+def test_gated_linear_attention_in_portions_and_far_memory(dtype, H, kd, vd):
+    """The kernel over a sequence cut into portions (a second request's rows in the same steps, its state in another slot)
+    against the plain mixer.  One key channel of head 0 never decays and holds a large key at position 2 only; the last
+    token asks for that channel alone: a state that is lost or decayed on the way shows in the last output."""
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * 100 + kd + vd)
+    L, R, tau, eps = 150, 5, 6.0, 1e-5
+    nq, nv = H * kd, H * vd
+    m = _gla(H, kd, vd, tau=tau)
+    width = 2 * nq + 2 * nv + R
+    W = _selectors(width, [("q", nq), ("k", nq), ("v", nv), ("g", nv), ("a1", R)])
+    W.update({"a2": _round(torch.randn(nq, R, generator=g), dtype), "a2.b": (torch.rand(nq, generator=g) * 6 - 1).double(),
+              "norm": (1 + 0.2 * torch.randn(vd, generator=g)).double(), "o": torch.eye(nv, dtype=torch.float64)})
+    u = _round(torch.randn(L, width, generator=g), dtype)
+    u[:, nq] = 0.0                                  # key channel 0 of head 0: silent but at position 2
+    u[2, nq] = 6.0
+    W["a2"][0] = 0.0
+    W["a2.b"][0] = 40.0                             # its gate is one
+    u[L - 1, :kd] = 0.0
+    u[L - 1, 0] = 8.0                               # the last query reads that channel alone
+    ref = plain.gated_linear_attention(u, W, "", m, eps)
+    other = _round(torch.randn(L, width, generator=g), dtype)
+    ref_other = plain.gated_linear_attention(other, W, "", m, eps)
+    dev = dict(device="cuda")
+    state = torch.zeros((3, H * kd * vd + 5), dtype=torch.float32, **dev)
+    power = torch.full((H,), 1.0 / tau, dtype=torch.float32, **dev)
+    bias = W["a2.b"].float().cuda()
+    norm_w = W["norm"].float().cuda()
+    got, got_other = torch.zeros(L, nv, dtype=torch.float64), torch.zeros(L, nv, dtype=torch.float64)
+    for i, fed, n in _portions(L, (37, 2, 16, 1, 50, 3)):
+        rows = torch.cat([u[fed:fed + n], other[fed:fed + n]])
+        x = rows.to(DT[dtype]).cuda()
+        low = (rows[:, -R:] @ W["a2"].T).to(DT[dtype]).cuda()
+        row_slot, row_last = _rows([n, n], [2, 0])
+        out = torch.empty((2 * n, nv), dtype=DT[dtype], **dev)
+        ops.gated_linear_attention(x[:, :2 * nq + nv], low, power, bias, x[:, 2 * nq + nv:2 * nq + 2 * nv], norm_w, eps,
+                                   kd ** -0.5, state, out, row_slot, row_last, H, kd, vd, requests=2)
+        got[fed:fed + n], got_other[fed:fed + n] = out[:n].double().cpu(), out[n:].double().cpu()
+    tol = MECH_TOL[dtype]
+    _close(got, ref, tol, "gated linear attention")
+    _close(got_other, ref_other, tol, "the request beside it")
+    _close(got[L - 1, :vd], ref[L - 1, :vd], tol, "the memory of position 2 at the last token")
+    assert float(state[1].abs().max()) == 0.0, "a slot that no request holds was written"
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,N,P,ng", [(4, 2, 16, 24, 2), (1, 1, 16, 16, 1), (6, 3, 10, 6, 3), (2, 1, 64, 64, 1), (4, 4, 128, 32, 4),
+                                        (6, 2, 32, 48, 2), (2, 2, 32, 128, 8)])
+def test_state_space_in_portions_and_far_memory(dtype, H, G, N, P, ng):
+    """Scan, skip, gate and norm in groups over a sequence cut into portions against the plain mixer (its convolution the
+    identity).  Head 0 hardly decays and takes a step of size one at position 3 only, where its input is large: what the
+    last token reads through the matching state channel is that input."""
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * 100 + N + P)
+    L, eps = 130, 1e-5
+    inner, gn = H * P, G * N
+    m = {"heads": H, "vdim": P, "state": N, "groups": G, "norm_groups": ng, "conv": 1}
+    width = 2 * inner + 2 * gn + H
+    W = {"in": torch.eye(width, dtype=torch.float64), "conv": torch.ones(inner + 2 * gn, 1, dtype=torch.float64),
+         "conv.b": torch.zeros(inner + 2 * gn, dtype=torch.float64), "dt_bias": (torch.rand(H, generator=g) * 3 - 3).double(),
+         "A_log": (torch.rand(H, generator=g) * 2 - 2).double(), "D": (1 + 0.3 * torch.randn(H, generator=g)).double(),
+         "norm": (1 + 0.2 * torch.randn(inner, generator=g)).double(), "o": torch.eye(inner, dtype=torch.float64)}
+    u = _round(torch.randn(L, width, generator=g), dtype)
+    W["A_log"][0] = -12.0                           # head 0 forgets nothing
+    W["dt_bias"][0] = 0.0
+    u[:, -H] = -30.0                                # and takes no step
+    u[3, -H] = 1.0                                  # but at position 3
+    u[3, inner:inner + P] = 5.0                     # where its input is large (before silu)
+    ref = plain.state_space_duality(u, W, "", m, eps)
+    dev = dict(device="cuda")
+    state = torch.zeros((2, H * N * P + 3), dtype=torch.float32, **dev)
+    a_log, dt_bias, skip, norm_w = (W[k].float().cuda() for k in ("A_log", "dt_bias", "D", "norm"))
+    got = torch.zeros(L, inner, dtype=torch.float64)
+    for i, fed, n in _portions(L, (41, 2, 16, 1, 33, 3)):
+        rows = u[fed:fed + n]
+        xbc = plain.silu(rows[:, inner:2 * inner + 2 * gn])
+        cbx = torch.cat([xbc[:, inner + gn:], xbc[:, inner:inner + gn], xbc[:, :inner]], dim=1).to(DT[dtype]).cuda()
+        z = rows[:, :inner].to(DT[dtype]).cuda()
+        dt = rows[:, -H:].to(DT[dtype]).cuda()
+        row_slot, row_last = _rows([n], [1])
+        raw = ops.state_space_scan(cbx, dt, a_log, dt_bias, state, row_slot, row_last, H, G, N, P, requests=1)
+        out = torch.empty((n, inner), dtype=DT[dtype], **dev)
+        ops.skip_gate_group_norm(raw, cbx[:, 2 * gn:], skip, z, norm_w, ng, eps, out, row_slot, H, P)
+        got[fed:fed + n] = out.double().cpu()
+    # the plain mixer rounds nothing between silu and the scan; in bfloat16 the kernel's input is the rounded silu
+    _close(got, ref, {"float32": 2e-5, "bfloat16": 5e-2}[dtype], "state space")
+    assert float(state[0].abs().max()) == 0.0
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dim,rot,page,scaling", [(4, 2, 16, 8, 16, (4.0, 64, 8.0, 1.0)), (2, 2, 24, 24, 4, None),
+                                                      (3, 1, 10, 4, 12, (2.0, 8, 2.0, 1.0)), (8, 1, 64, 32, 16, (2.0, 32, 4.0, 0.5)),
+                                                      (4, 1, 96, 24, 16, None), (2, 2, 128, 128, 32, (8.0, 100, 16.0, 2.0))])
+def test_tied_value_attention_sink_and_a_key_far_back(dtype, H, G, dim, rot, page, scaling):
+    """Rotation, cache write and attention over scattered pages, a sequence cut into portions and single rows, against the
+    plain mixer.  The key at position 1 and the last query are scaled so that their score stands out among hundreds; head
+    0's sink is large, so that leaving it out doubles head 0's output; the values must be the unrotated keys."""
+    from tiny_inference_server_b200.kernels import ops
+    from tiny_inference_server_b200.parts.positions import RotaryRescaled
+    g = torch.Generator().manual_seed(H * 10 + dim)
+    L = 300
+    m = _par(H, G, dim, rot, 1, 1, 1, 1, 1, 1, scaling=scaling, scale=0.5 * dim ** -0.5)["left"]
+    nq, nk = H * dim, G * dim
+    W = _selectors(nq + nk, [("q", nq), ("k", nk)])
+    W["o"] = torch.eye(nq, dtype=torch.float64)
+    W["sink"] = torch.randn(H, generator=g).double()
+    W["sink"][0] = 3.0
+    u = _round(torch.randn(L, nq + nk, generator=g), dtype)
+    u[1, nq:nq + dim] *= 3.0
+    u[L - 1, :dim] = u[1, nq:nq + dim] * 0.7         # the last query of head 0 looks like the key at position 1 (unrotated part)
+    ref = plain.sink_attention(u, W, "", m)
+    pos = RotaryRescaled(dim, m["rot"]["base"], L + 8, scaling=m["rot"].get("scaling"), rotary_dim=rot)
+    cos, sin = (t.cuda() for t in pos.tables())
+    n_pages = (L + page - 1) // page + 3
+    perm = torch.randperm(n_pages, generator=g)[: (L + page - 1) // page].to(torch.int32)
+    table = torch.full((3, len(perm) + 2), -1, dtype=torch.int32)
+    table[1, :len(perm)] = perm
+    table = table.cuda()
+    dev = dict(device="cuda")
+    k_pages = torch.full((n_pages, G, page, dim), 7.0, dtype=DT[dtype], **dev)
+    v_pages = torch.full((n_pages, G, page, dim), 7.0, dtype=DT[dtype], **dev)
+    fault = torch.zeros(4, dtype=torch.int32, **dev)
+    sink = W["sink"].float().cuda()
+    got = torch.zeros(L, nq, dtype=torch.float64)
+    for i, fed, n in _portions(L, (70, 2, 16, 1, 100, 3), alone=6):
+        qk = u[fed:fed + n].to(DT[dtype]).cuda()
+        positions = torch.arange(fed, fed + n, dtype=torch.int32, **dev)
+        row_slot, _ = _rows([n], [1])
+        ops.rotate_tie_store(qk, H, G, dim, rot, cos, sin, k_pages, v_pages, table, positions, row_slot, page, fault)
+        out = torch.empty((n, nq), dtype=DT[dtype], **dev)
+        step = _Step(positions, row_slot, decode_only=(n == 1))
+        ops.window_attention(qk[:, :nq], None, out, k_pages, v_pages, table, positions, row_slot, H, page, None, m["scale"],
+                             None, None, fault, step, sink=sink)
+        got[fed:fed + n] = out.double().cpu()
+    assert int(fault[0]) == 0
+    tol = MECH_TOL[dtype]
+    _close(got, ref, tol, "attention with tied values")
+    _close(got[L - 1, :dim], ref[L - 1, :dim], tol, "the last query, which looks far back")
+    no_sink = dict(W, sink=torch.full((H,), -1e9, dtype=torch.float64))
+    assert float((plain.sink_attention(u, no_sink, "", m)[:, :dim] - ref[:, :dim]).abs().max()) > 10 * tol * float(ref.abs().max())
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,d,groups", [(37, 64, 4), (5, 40, 1), (130, 192, 2), (1, 1000, 8), (3, 96, 48), (2, 30, 30)])
+def test_norm_in_groups_with_two_updates_and_two_outputs(dtype, n, d, groups):
+    import kernel_refs
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(n + d)
+    res = torch.randn(n, d, generator=g) * 3
+    da, db = (torch.randn(n, d, generator=g).to(DT[dtype]) for _ in range(2))
+    w1, w2 = (1 + 0.2 * torch.randn(d, generator=g) for _ in range(2))
+    want_res = res.clone()
+    o1, o2 = torch.empty(n, d), torch.empty(n, d)
+    kernel_refs.group_norm(want_res, da, db, groups, 1e-5, w1, o1, w2, o2)
+    r = res.cuda()
+    a, b = torch.empty(n, d, dtype=DT[dtype], device="cuda"), torch.empty(n, d, dtype=DT[dtype], device="cuda")
+    ops.group_norm(r, da.cuda(), db.cuda(), groups, 1e-5, w1.cuda(), a, w2.cuda(), b)
+    tol = {"float32": 1e-5, "bfloat16": 1e-2}[dtype]
+    _close(r, want_res.double(), 1e-6, "the stream with both updates")
+    _close(a, o1.double(), tol, "first output")
+    _close(b, o2.double(), tol, "second output")
+    # one update, one output; then the stream itself replaced by its norm
+    r2 = res.cuda()
+    ops.group_norm(r2, None, db.cuda(), groups, 1e-5, w1.cuda(), a)
+    want2 = res.clone()
+    kernel_refs.group_norm(want2, None, db, groups, 1e-5, w1, o1)
+    _close(a, o1.double(), tol, "one update")
+    ops.group_norm(r2, None, None, groups, 1e-5, w2.cuda(), None, in_place=True)
+    kernel_refs.group_norm(want2, None, None, groups, 1e-5, w2, None, in_place=True)
+    _close(r2, want2.double(), 1e-5, "in place")
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pair_embedding_carries_the_previous_token(dtype):
+    """Portions of two requests side by side, one of them from its first token: the row of the pair table comes from the
+    token before, which lies in the same step, in the request's state, or nowhere."""
+    import kernel_refs
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(1)
+    vocab, d, buckets = 50, 40, 13
+    table, pairs = torch.randn(vocab, d, generator=g).to(DT[dtype]), torch.randn(buckets + 1, d, generator=g).to(DT[dtype])
+    seq_a, seq_b = torch.randint(0, vocab, (20,), generator=g).tolist(), torch.randint(0, vocab, (9,), generator=g).tolist()
+    prev_dev = torch.zeros((3, 1), dtype=torch.int32, device="cuda")
+    prev_ref = torch.zeros((3, 1), dtype=torch.int32)
+    fed = {"a": 0, "b": 0}
+    for na, nb in ((3, 0), (1, 2), (7, 1), (1, 1), (8, 5)):
+        toks, poss, cuts, slots = [], [], [], []
+        for rid, seq, n, slot in (("a", seq_a, na, 2), ("b", seq_b, nb, 0)):
+            if n:
+                toks += seq[fed[rid]:fed[rid] + n]
+                poss += list(range(fed[rid], fed[rid] + n))
+                cuts.append(n)
+                slots.append(slot)
+                fed[rid] += n
+        row_slot, row_last = _rows(cuts, slots)
+        t = torch.tensor(toks, dtype=torch.int32)
+        p = torch.tensor(poss, dtype=torch.int32)
+        out = torch.empty((len(toks), d), dtype=torch.float32, device="cuda")
+        ops.embed_pairs(table.cuda(), pairs.cuda(), t.cuda(), p.cuda(), row_slot, row_last, prev_dev, out, 2.5, buckets, 31, 7)
+        want = torch.empty((len(toks), d), dtype=torch.float32)
+        kernel_refs.embed_pairs(table, pairs, t, p, row_slot.cpu(), row_last.cpu(), prev_ref, want, 2.5, buckets, 31, 7)
+        _close(out, want.double(), 1e-6, f"portion {na}, {nb}")
+        assert prev_dev.cpu().tolist() == prev_ref.tolist()
+    whole = plain.embed({"embedding": {"scale": 2.5, "bigram": {"buckets": buckets, "mul_prev": 31, "mul_cur": 7}}},
+                        {"embed": table.double(), "bigram": pairs.double()}, seq_a[-8:])
+    _close(out[:8][1:], whole[1:], 1e-6, "against the plain embedding")
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,d,F,E,top", [(3, 48, 40, 6, 2), (1, 64, 96, 16, 4), (40, 64, 32, 8, 3), (300, 128, 64, 8, 4),
+                                         (700, 192, 96, 16, 4), (50, 40, 24, 5, 5)])
+def test_routed_experts_without_gates(dtype, n, d, F, E, top):
+    """Router (the largest logits choose, the softmax over the chosen weighs) and experts ``W_down relu(W_up h)^2`` for few
+    rows (a dot product per element), for a hundred pairs (tiles on the tensor cores) and for a thousand (tcgen05 tiles)."""
+    import kernel_refs
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(n + d)
+    x = torch.randn(n, d, generator=g).to(DT[dtype])
+    wr = torch.randn(E, d, generator=g) * 4 / math.sqrt(d)
+    up = (torch.randn(E, F, d, generator=g) / math.sqrt(d)).to(DT[dtype])
+    down = (torch.randn(E, d, F, generator=g) / math.sqrt(F)).to(DT[dtype])
+    chosen, weights, _ = ops.moe_route(x.cuda(), wr.cuda(), None, None, 0, 0, top, scores="softmax_chosen")
+    ref_chosen, ref_weights, _ = kernel_refs.moe_route(x, wr, None, None, 0, 0, top, scores="softmax_chosen")
+    logits = x.float() @ wr.t()
+    gap = logits.topk(min(top + 1, E), dim=-1).values
+    clear = (gap[:, :-1] - gap[:, 1:]).min(-1).values > 1e-3 if top < E else torch.ones(n, dtype=torch.bool)
+    assert (chosen.cpu()[clear].sort(-1).values == ref_chosen[clear].sort(-1).values).all()
+    _close(weights.cpu()[clear].sort(-1).values, ref_weights[clear].sort(-1).values.double(), 1e-4, "weights")
+    assert float((weights.sum(-1) - 1).abs().max()) < 1e-5
+    before = dict(ops.calls)
+    out = ops.moe_experts(x.cuda(), chosen, weights, up.cuda(), down.cuda(), None, None, act="relu2")
+    want = kernel_refs.moe_experts(x.float(), chosen.cpu(), weights.cpu(), up.float(), down.float(), None, None, act="relu2")
+    _close(out, want.double(), {"float32": 2e-5, "bfloat16": 3e-2}[dtype], "experts")
+    if dtype == "bfloat16" and n * top >= 1024 and d % 64 == 0 and F % 64 == 0:
+        assert ops.calls["moe_grouped_tc"] == before.get("moe_grouped_tc", 0) + 1
+    elif dtype == "bfloat16" and n * top >= 96 and d % 32 == 0 and F % 32 == 0:
+        assert ops.calls["moe_grouped"] == before.get("moe_grouped", 0) + 1
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("c,taps", [(40, 4), (13, 2), (64, 1), (24, 7)])
+def test_short_convolution_with_a_bias(dtype, c, taps):
+    import kernel_refs
+    from tiny_inference_server_b200.kernels import ops
+    g = torch.Generator().manual_seed(c)
+    w, bias = torch.randn(taps, c, generator=g), torch.randn(c, generator=g)
+    x = torch.randn(30, c, generator=g).to(DT[dtype])
+    st_dev, st_ref = torch.zeros((2, max(1, (taps - 1) * c) + 2), device="cuda"), torch.zeros((2, max(1, (taps - 1) * c) + 2))
+    for fed, n in ((0, 2), (2, 1), (3, 11), (14, 1), (15, 15)):
+        row_slot, row_last = _rows([n], [1])
+        out = torch.empty((n, c), dtype=DT[dtype], device="cuda")
+        ops.causal_conv(x[fed:fed + n].cuda(), w.cuda(), st_dev, out, row_slot, row_last, silu=True, bias=bias.cuda())
+        want = torch.empty((n, c), dtype=DT[dtype])
+        kernel_refs.causal_conv(x[fed:fed + n], w, st_ref, want, row_slot.cpu(), row_last.cpu(), silu=True, bias=bias)
+        _close(out, want.double(), {"float32": 1e-5, "bfloat16": 1e-2}[dtype], f"rows {fed}..{fed + n}")
+
+
+# ------------------------------------------------------------------------------------------------
+# whole models on the device
+# ------------------------------------------------------------------------------------------------
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+def test_replay_gpu(name, mode, dtype, tmp_path, tmp_path_factory):
+    raw, page, folder, seqs, ref, _, _ = _setup(name, tmp_path_factory)
+    steps = _steps(mode, seqs, max_live=3)
+    runner, _ = _replay_and_compare(raw, page, folder, seqs, ref, steps, str(tmp_path / "out"), dtype, "cuda:0", TOL[dtype],
+                                    max_live=3, poison=(mode == "mixed"), shuffle=(mode == "mixed"), outliers=BF16_OUTLIERS[dtype])
+    if mode == "mixed" and name == "K1":          # its requests are long enough for the pool to turn over
+        pool = runner.cache.groups[0].pool
+        assert pool.allocations > pool.num_pages, "the trace does not use pages again"
+
+
+@gpu
+@pytest.mark.parametrize("name", ["K1", "K3"])
+def test_layers_of_the_stream_gpu(name, tmp_path_factory):
+    """The residual stream after every layer run in float32 on the device against the plain layers."""
+    raw, page, folder, seqs, _, c, W = _setup(name, tmp_path_factory)
+    _check_layers(folder, page, seqs["r3"], c, W, "cuda:0")
+
+
+def random_configuration(seed):
+    """A configuration drawn at random: layer order, loop, head counts, widths, taps, groups, constants, all of it."""
+    import random
+    rng = random.Random(seed)
+    pick = rng.choice
+    width = pick([24, 32, 48, 64, 96, 128, 192])
+    layers = []
+    kinds = ["gla", "parallel"]
+    rng.shuffle(kinds)
+    for kind in kinds + [pick(kinds) for _ in range(rng.randint(0, 3))]:
+        if kind == "gla":
+            mixer = _gla(pick([1, 2, 3, 4]), pick([8, 16, 32, 48, 64]), pick([8, 16, 32, 64, 96]), tau=pick([1.0, 4.0, 16.0, 64.0]))
+        else:
+            kv = pick([1, 2, 3])
+            dim = pick([8, 16, 24, 32, 64, 96])
+            rot = pick([d for d in (4, 8, 16, 24, 32, 64) if d <= dim] + [dim])
+            groups = pick([1, 2, 3])
+            heads = groups * pick([1, 2, 3])
+            vdim = pick([8, 16, 24, 48, 64])
+            ng = pick([n for n in (1, 2, 3, 4, 6) if (heads * vdim) % n == 0])
+            mixer = _par(kv * pick([1, 2, 4]), kv, dim, rot, heads, vdim, pick([8, 16, 32, 64]), groups, ng, pick([2, 3, 4]),
+                         base=pick([100.0, 10000.0, 1e6]), scaling=pick([None, (2.0, 64, 8.0, 1.0), (16.0, 32, 32.0, 2.0)]),
+                         scale=pick([None, 0.2]), left_scale=pick([0.5, 1.0, 1.2]), right_scale=pick([0.7, 1.0, 1.1]))
+        r = rng.random()
+        mlp = None if r < 0.15 else (_dense(pick([24, 32, 64, 100, 256])) if r < 0.55 else
+                                     _moe(pick([16, 32, 64, 96]), *pick([(4, 1), (4, 2), (8, 2), (16, 4), (6, 3), (3, 3)])))
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    n = len(layers)
+    start = rng.randint(0, n - 1)
+    loop = (start, rng.randint(start, n), rng.randint(1, 3)) if rng.random() < 0.8 else None
+    groups = pick([g for g in (1, 2, 3, 4, 8) if width % g == 0])
+    cfg = _cfg(rng.randint(40, 300), width, layers, groups=groups, taps=pick([1, 2, 3, 4, 5]), buckets=pick([1, 17, 509, 4099]),
+               muls=(pick([0, 1, 127, 100003]), pick([1, 17, 31])), scale=pick([0.5, 1.0, 8.0, 13.9]), loop=loop,
+               eps=pick([1e-5, 1e-6]))
+    return cfg, pick([8, 16, 16, 32])
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_configurations_drawn_at_random(seed, dtype, tmp_path):
+    """Whatever config.json says runs without a change of code: configurations drawn at random, a mixed batch of five
+    requests (one of them long) through three slots over shuffled pages (``BF16_OUTLIERS``)."""
+    raw, page = random_configuration(seed)
+    folder = make_folder(raw, 100 + seed, str(tmp_path / "m"))
+    c, W = read_folder(folder)
+    g = torch.Generator().manual_seed(seed)
+    seqs = {f"r{i}": torch.randint(0, raw["vocab"], (n,), generator=g).tolist() for i, n in enumerate([1, 2, 45, 400, 130])}
+    ref = {rid: plain.plain_forward(c, W, toks).numpy() for rid, toks in seqs.items()}
+    steps = trace_tools.trace_mixed(seqs, max_live=3, prefill_sizes=(64, 2, 130, 17))
+    _replay_and_compare(raw, page, folder, seqs, ref, steps, str(tmp_path / "out"), dtype, "cuda:0", TOL[dtype], max_live=3,
+                        poison=True, shuffle=True, outliers=BF16_OUTLIERS[dtype])
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_slots_used_again_and_again(dtype, tmp_path, tmp_path_factory):
+    """Eight requests through two state slots: a state, a convolution's history or a previous token that is not cleared
+    when its slot is given to the next request shows in that request's first tokens."""
+    raw, page, folder, seqs, ref, _, _ = _setup("K1", tmp_path_factory)
+    steps = trace_tools.trace_mixed(seqs, max_live=2, prefill_sizes=(2, 7, 3, 2), skip_every=4)
+    _replay_and_compare(raw, page, folder, seqs, ref, steps, str(tmp_path / "out"), dtype, "cuda:0", TOL[dtype], max_live=2,
+                        poison=True, outliers=BF16_OUTLIERS[dtype])
+
+
+@gpu
+@pytest.mark.parametrize("name", ["K1", "K4"])
+def test_long_decoding_float32(name, tmp_path, tmp_path_factory):
+    """A short prompt, then 300 tokens one by one, replayed from a graph: the states carry what hundreds of decode steps
+    wrote and every step's attention reads the whole cache."""
+    raw, page, folder, _, _, c, W = _setup(name, tmp_path_factory)
+    g = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, raw["vocab"], (305,), generator=g).tolist()
+    ref = {"a": plain.plain_forward(c, W, toks).numpy()}
+    steps = trace_tools.trace_tail({"a": toks}, tail=300)
+    runner = make_runner(folder, "float32", 320, page_size=page, max_live=1, debug_poison=True)
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir).run(json.dumps(s) for s in steps)
+    assert runner.cache.drained()
+    assert runner.graphs is not None and runner.graphs.replays > 250
+    got = trace_tools.gather(steps, out_dir, raw["vocab"])
+    for p in range(len(toks)):
+        assert rel_err(got["a"][p], ref["a"][p]) < TOL["float32"], f"position {p}"
+
+
+@gpu
+def test_generate_through_the_scheduler(tmp_path, tmp_path_factory):
+    raw, page, folder, seqs, _, c, W = _setup("K3", tmp_path_factory)
+    prompts = [seqs["r0"], seqs["r4"], seqs["r1"], seqs["r5"]]
+    want = [plain_greedy(c, W, p, 10) for p in prompts]
+    sp = SamplingParams(max_new_tokens=10, temperature=0.0, ignore_eos=True)
+    for kw in (dict(max_batch=4, max_tokens_per_step=2048), dict(max_batch=2, max_tokens_per_step=9)):
+        eng = Engine.from_folder(folder, EngineConfig(dtype="float32", page_size=page, num_pages=40, **kw))
+        assert eng.generate(prompts, sp) == want
+        assert eng.runner.cache.drained()
+    eng = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_size=page, num_pages=40, max_batch=4))
+    out = eng.generate(prompts, sp)
+    assert [len(o) for o in out] == [10] * 4 and eng.runner.cache.drained()
+
+
+@gpu
+def test_command_line_generation_with_chunking_and_preemption(tmp_path, tmp_path_factory):
+    """Greedy tokens through ``python -m tiny_inference_server_b200.cli`` equal the plain implementation's: whole
+    prompts; a token budget of five (portions beside decoding requests); and so few pages that requests are preempted
+    and fed again from their first token (their states, histories and previous tokens start from nothing again)."""
+    from test_cli import _cli, _ids
+    raw, page, folder, seqs, _, c, W = _setup("K1", tmp_path_factory)
+    new = 8
+    prompts = [seqs["r0"], seqs["r6"], seqs["r1"]]
+    want = [plain_greedy(c, W, p, new) for p in prompts]
+    args = ["--model", folder, "--greedy", "--ignore-eos", "--dtype", "float32", "--max-new-tokens", new,
+            "--tokens-per-block", page, "--json"]
+    for p in prompts:
+        args += ["--prompt-ids", _ids(p)]
+    r = _cli(*args)
+    assert r.returncode == 0, r.stderr
+    assert json.loads(r.stdout.strip().splitlines()[-1])["outputs"] == want
+    r = _cli(*args, "--max-tokens-per-step", 5, "--max-batch", 2)
+    assert r.returncode == 0, r.stderr
+    assert json.loads(r.stdout.strip().splitlines()[-1])["outputs"] == want
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, raw["vocab"], (page - 1,), generator=g).tolist() for _ in range(4)]
+    want = [plain_greedy(c, W, p, new) for p in prompts]
+    args = ["--model", folder, "--greedy", "--ignore-eos", "--dtype", "float32", "--max-new-tokens", new,
+            "--tokens-per-block", page, "--json", "--num-pages", 5, "--plan", "cur", "--max-batch", 4,
+            "--max-tokens-per-step", 16]
+    for p in prompts:
+        args += ["--prompt-ids", _ids(p)]
+    r = _cli(*args)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["outputs"] == want
+    assert out["stats"]["preempts"] > 0 and out["stats"]["replays"] > 0
