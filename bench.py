@@ -440,6 +440,84 @@ def compare_biruvik(args):
     return 0
 
 
+def kubolorn_config(width, heads, kv_heads, ffn, vocab, layers, experts=16, top=4):
+    """A Kubolorn model with the layer sizes of a member of the GQA family: per four layer runs three of gated linear
+    attention and one of attention with tied values beside a selective state space, keys, values and states of 128
+    elements; feed-forwards in turn dense (1.5 ffn hidden elements without a gate: as many weights as the gated one of
+    ffn) and routed (``top`` of ``experts`` ungated experts that together hold as many weights a token); two of the layers
+    run twice in a row, so that ``layers`` layer runs come from ``layers - 2`` layers' weights."""
+    fd = ffn * 3 // 2 // 64 * 64
+    fe = max(64, ffn * 3 // 2 // top // 64 * 64)
+    gla = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": heads, "vdim": 128, "state": 128, "groups": kv_heads, "norm_groups": kv_heads, "conv": 4},
+           "left_scale": 1.0, "right_scale": 1.0}
+    dense = {"kind": "dense", "ff": fd}
+    moe = {"kind": "moe", "expert": {"ff": fe}, "router": {"experts": experts, "top": top}}
+    n = max(3, layers - 2)
+    kinds = [("gla", gla, dense), ("gla", gla, moe), ("gla", gla, dense), ("parallel", par, moe)]
+    return dict(architecture="Kubolorn", vocab=vocab, width=width, norm={"eps": 1e-6, "groups": 2}, max_context=8192,
+                embedding={"scale": width ** 0.5, "bigram": {"buckets": 4099, "mul_prev": 127, "mul_cur": 17}},
+                canon={"taps": 4}, loop={"start": 1, "stop": 3, "times": 2},
+                layers=[{"type": kinds[i % 4][0], "mixer": json.loads(json.dumps(kinds[i % 4][1])),
+                         "mlp": json.loads(json.dumps(kinds[i % 4][2]))} for i in range(n)])
+
+
+def compare_kubolorn(args):
+    """``--compare kubolorn``: prefill and decode of the Kubolorn architecture beside the Mizidra architecture (the closest
+    earlier one: recurrent layers with a matrix state beside attention layers, routed experts), the Kefisun architecture
+    (short convolutions in front of the sublayers) and the rotary GQA model at equal layer sizes and layer runs, and its
+    kernels beside the like kernels of those.  One JSON line; the default run is untouched."""
+    import gc
+    import types
+    import torch
+    from tiny_inference_server_b200.kernels import microbench, ops
+    from tiny_inference_server_b200.sampling import Sampler
+    pk = peaks()
+    count_ops = lambda: ops.launches  # noqa: E731
+    window, ctx, layers = 4096, 4096, 8
+    result = {"compare": "kubolorn", "dtype": "bf16", "data": "synthetic", "layers": layers, "context": ctx, "peaks": pk,
+              "sizes": {}}
+    for name in [x for x in args.compare_sizes.split(",") if x]:
+        base = SIZES[name][0]
+        twin = dict(base, num_layers=layers, num_mtp_heads=0, max_context=8192, tie_word_embeddings=True)
+        size = (base["hidden_size"], base["num_heads"], base["num_kv_heads"], base["ffn_hidden"], base["vocab_size"], layers)
+        point = {}
+        for label, cfg_dict in (("kubolorn", kubolorn_config(*size)), ("mizidra", mizidra_config(*size)),
+                                ("kefisun", kefisun_config(*size, window)), ("gqa", twin)):
+            runner = None
+            try:
+                _, runner = build_runner(cfg_dict, ctx, 8, mtp=False)
+                steps = max(8, args.steps // 2)
+                r = {}
+                for b in (1, 8):
+                    ms, launches = decode_run(runner, b, ctx - steps - args.warmup - 2, steps, args.warmup, Sampler, count_ops)
+                    r[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    r[f"decode_b{b}_ms"] = round(ms, 4)
+                    r[f"decode_b{b}_launches"] = round(launches, 1)
+                best, first = prefill_run(runner, PREFILL_TOKENS, reps=2)
+                r["prefill_tok_s"] = round(PREFILL_TOKENS / (best * 1e-3), 1)
+                r["prefill_ms"] = round(best, 3)
+                r["prefill_first_run_ms"] = round(first, 3)
+                point[label] = r
+            except Exception as e:                       # noqa: BLE001
+                point[label] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        margs = types.SimpleNamespace(width=base["hidden_size"], ffn=base["ffn_hidden"], heads=base["num_heads"],
+                                      kv_heads=base["num_kv_heads"], head_dim=128, page_size=PAGE, tokens=PREFILL_TOKENS, batch=8,
+                                      context=ctx, experts=16, top=4)
+        try:
+            point["kernels"] = microbench.gated_space_tied(margs)
+        except Exception as e:                           # noqa: BLE001
+            point["kernels"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        result["sizes"][name] = point
+    print(json.dumps(result))
+    return 0
+
+
 def compare_kefisun(args):
     """``--compare kefisun``: prefill and decode of the Kefisun architecture beside the rotary GQA model at equal
     layer sizes (same width, heads, feed-forward, vocabulary, number of layers, and the same window of keys), and
@@ -585,7 +663,7 @@ def main(argv=None):
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, other contexts, MTP heads and prefill")
     ap.add_argument("--sizes", default="3b,8b", help="larger members of the family to measure too (3b, 8b; '' = none)")
-    ap.add_argument("--compare", default=None, choices=["kefisun", "mizidra", "biruvik"],
+    ap.add_argument("--compare", default=None, choices=["kefisun", "mizidra", "biruvik", "kubolorn"],
                     help="instead of the default run: another architecture beside the GQA model at equal layer sizes")
     ap.add_argument("--compare-sizes", default="0.9b,3b", help="with --compare: whose layer sizes (0.9b, 3b, 8b)")
     args = ap.parse_args(argv)
@@ -597,6 +675,8 @@ def main(argv=None):
     if args.compare == "mizidra":
         args.warmup = max(args.warmup, 3)
         return compare_mizidra(args)
+    if args.compare == "kubolorn":
+        return compare_kubolorn(args)
     if args.compare == "biruvik":
         args.warmup = max(args.warmup, 3)
         return compare_biruvik(args)

@@ -583,6 +583,172 @@ def differential_latent_forget(args):
     return out
 
 
+def gated_space_tied(args):
+    """The kernels of gated linear attention, of a selective state space (scan; skip, gate and norm in groups), of attention
+    whose values are its keys (rotation and cache write; attention with a keyless softmax term), of the norm in groups with
+    two updates and two outputs, of the embedding with a hashed second table and of routed experts without gates, each
+    beside the kernel of an earlier architecture of this engine that does the like work at equal sizes.  Sizes: ``heads``
+    heads with keys and values of ``head_dim`` for the recurrences and the attention (``kv_heads`` key heads), a state of
+    ``head_dim`` per head for the state space.  Returns {name: {us, rate, unit, like_us, like_rate}}."""
+    dev = "cuda"
+    d, F, H, G, hd, page = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, B, ctx = args.tokens, args.batch, args.context
+    E, top = args.experts, args.top
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    i32 = dict(device=dev, dtype=torch.int32)
+    fault = torch.zeros(4, **i32)
+    out = {}
+
+    def put(name, us, work, unit, like_us=None, like_work=None):
+        e = {"us": round(us, 2), "rate": round(work / us / 1e3, 1) if unit == "GB/s" else round(work / us / 1e6, 1), "unit": unit}
+        if like_us is not None:
+            lw = work if like_work is None else like_work
+            e["like_us"] = round(like_us, 2)
+            e["like_rate"] = round(lw / like_us / 1e3, 1) if unit == "GB/s" else round(lw / like_us / 1e6, 1)
+        out[name] = e
+        like = f"   like kernel {e['like_us']:9.2f} us {e['like_rate']:9.1f} {unit}" if like_us is not None else ""
+        print(f"{name:52s} {e['us']:9.2f} us {e['rate']:9.1f} {unit}{like}")
+
+    pos, slot = torch.arange(n, **i32), torch.zeros(n, **i32)
+    last = torch.full((n,), n - 1, **i32)
+    slot_b = torch.arange(B, **i32)
+    one = (torch.zeros(1, **i32), 1)
+    nv = H * hd
+    # ---- gated linear attention beside the recurrence whose forget gate writes (the same walk of a matrix state with a
+    # gate per key channel; this one also reads keys) and, for decode rows, the same
+    rows = [torch.randn(n, 4 * nv, **bf) for _ in range(2)]
+    power, a_bias, nw = torch.full((H,), 1 / 16, device=dev), torch.full((nv,), 3.0, device=dev), torch.ones(hd, device=dev)
+    lower, fb = torch.rand(nv, device=dev) * 0.9, torch.zeros(nv, device=dev)
+    gate = torch.randn(n, nv, **bf)
+    st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
+    od = torch.empty(n, nv, **bf)
+    t_new = _graph_time(lambda i: ops.gated_linear_attention(rows[i % 2][:, :3 * nv], rows[i % 2][:, 3 * nv:], power, a_bias, gate, nw,
+                                                             1e-6, hd ** -0.5, st, od, slot, last, H, hd, hd, requests=1, segments=one), 4)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.forget_gate_recurrence(rows[i % 2][:, :2 * nv], rows[i % 2][:, 2 * nv:3 * nv], lower, fb, nw, 1e-6,
+                                                              st, od, slot, last, H, hd, hd, requests=1, segments=one), 4)
+    put(f"gated linear attention, {n} rows", t_new, 4.0 * n * H * hd * hd, "TFLOP/s", t_like)
+    st.zero_()
+    t_new = _graph_time(lambda i: ops.gated_linear_attention(rows[i % 2][:B, :3 * nv], rows[i % 2][:B, 3 * nv:], power, a_bias, gate[:B],
+                                                             nw, 1e-6, hd ** -0.5, st, od[:B], slot_b, slot_b, H, hd, hd, requests=B,
+                                                             segments=(slot_b, B)), 12)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.forget_gate_recurrence(rows[i % 2][:B, :2 * nv], rows[i % 2][:B, 2 * nv:3 * nv], lower, fb, nw,
+                                                              1e-6, st, od[:B], slot_b, slot_b, H, hd, hd, requests=B,
+                                                              segments=(slot_b, B)), 12)
+    put(f"gated linear attention, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s", t_like)
+    # ---- the state space's scan (input and output matrices of G groups, a step size per head) beside the delta rule with
+    # one decay per head (the same decay; it also corrects the state towards the value)
+    gn = G * hd
+    cbx = [torch.randn(n, 2 * gn + nv, **bf) for _ in range(2)]
+    dt = torch.randn(n, H, **bf)
+    a_log, dt_bias = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+    beta = torch.randn(n, H, **bf)
+    st.zero_()
+    t_new = _graph_time(lambda i: ops.state_space_scan(cbx[i % 2], dt, a_log, dt_bias, st, slot, last, H, G, hd, hd, requests=1,
+                                                       segments=one), 4)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.delta_rule(cbx[i % 2], beta, dt, gate, a_log, dt_bias, nw, 1e-6, 1e-6, hd ** -0.5, st, od, slot,
+                                                  last, H, G, hd, hd, requests=1, segments=one, decay_per_head=True), 4)
+    put(f"state space scan, {n} rows", t_new, 4.0 * n * H * hd * hd, "TFLOP/s", t_like, 6.0 * n * H * hd * hd)
+    st.zero_()
+    t_new = _graph_time(lambda i: ops.state_space_scan(cbx[i % 2][:B], dt[:B], a_log, dt_bias, st, slot_b, slot_b, H, G, hd, hd,
+                                                       requests=B, segments=(slot_b, B)), 12)
+    st.zero_()
+    t_like = _graph_time(lambda i: ops.delta_rule(cbx[i % 2][:B], beta[:B], dt[:B], gate[:B], a_log, dt_bias, nw, 1e-6, 1e-6, hd ** -0.5,
+                                                  st, od[:B], slot_b, slot_b, H, G, hd, hd, requests=B, segments=(slot_b, B),
+                                                  decay_per_head=True), 12)
+    put(f"state space scan, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s", t_like)
+    bufs = 4
+    raw = [torch.randn(n, nv, device=dev) for _ in range(bufs)]
+    skip, nwl = torch.ones(H, device=dev), torch.ones(nv, device=dev)
+    t_new = _graph_time(lambda i: ops.skip_gate_group_norm(raw[i % bufs], cbx[i % 2][:, 2 * gn:], skip, gate, nwl, 2, 1e-6, od, slot, H, hd), 12)
+    mp = [torch.randn(n, 2 * nv, **bf) for _ in range(bufs)]
+    t_like = _graph_time(lambda i: ops.diff_combine(mp[i % bufs], 0.8, 1e-6, 0.7, od, H, hd, slot), 12)
+    put(f"skip, gate, norm in groups, {n} rows", t_new, n * nv * (4 + 2 * 3), "GB/s", t_like, n * 3 * nv * 2)
+    # ---- attention with tied values: rotation and cache write beside the norm-and-store of windowed attention; attention
+    # with the keyless term beside the same kernel without it
+    num_pages = (n + page - 1) // page
+    kp, vp = torch.zeros(num_pages, G, page, hd, **bf), torch.zeros(num_pages, G, page, hd, **bf)
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    nq, nk = H * hd, G * hd
+    qk = [torch.randn(n, nq + 2 * nk, **bf) for _ in range(bufs)]
+    rot = hd // 4
+    cos, sin = torch.ones(n, rot // 2, device=dev), torch.zeros(n, rot // 2, device=dev)
+    t_new = _graph_time(lambda i: ops.rotate_tie_store(qk[i % bufs], H, G, hd, rot, cos, sin, kp, vp, table, pos, slot, page, fault), 12)
+    wq, wk = torch.ones(nq, device=dev), torch.ones(nk, device=dev)
+    t_like = _graph_time(lambda i: ops.norm_mix_store(qk[i % bufs], nq, nk, nk, wq, wk, 1e-6, None, None, kp, vp, table, pos, slot, page,
+                                                      fault), 12)
+    put(f"rotation and tied cache write, {n} rows", t_new, n * (2 * H * rot + nk + 2 * nk) * 2, "GB/s", t_like, n * (nq + 2 * nk) * 2 * 2)
+    step = _PortionStep(pos, slot)
+    pairs = n * (n + 1) // 2
+    kps = [torch.randn(num_pages, G, page, hd, **bf) for _ in range(2)]
+    vps = [torch.randn(num_pages, G, page, hd, **bf) for _ in range(2)]
+    q, o = torch.randn(n, nq, **bf), torch.empty(n, nq, **bf)
+    sink = torch.zeros(H, device=dev)
+    t_new = _graph_time(lambda i: ops.window_attention(q, None, o, kps[i % 2], vps[i % 2], table, pos, slot, H, page, None, hd ** -0.5,
+                                                       None, None, fault, step, sink=sink), 6)
+    t_like = _graph_time(lambda i: ops.window_attention(q, None, o, kps[i % 2], vps[i % 2], table, pos, slot, H, page, None, hd ** -0.5,
+                                                        None, None, fault, step), 6)
+    put(f"attention with a keyless term, {n} rows", t_new, 4.0 * H * hd * pairs, "TFLOP/s", t_like)
+    pages_per = (ctx + page - 1) // page
+    n_bufs = max(2, min(12, (300 << 20) // max(1, B * ctx * 2 * G * hd * 2)))
+    kps = [torch.randn(B * pages_per, G, page, hd, **bf) for _ in range(n_bufs)]
+    vps = [torch.randn(B * pages_per, G, page, hd, **bf) for _ in range(n_bufs)]
+    dtable = torch.arange(B * pages_per, **i32).reshape(B, pages_per).contiguous()
+    pos_b = torch.full((B,), ctx - 1, **i32)
+    dstep = _PortionStep(pos_b, slot_b, decode=True)
+    qd, odd = q[:B].contiguous(), o[:B].contiguous()
+    t_new = _graph_time(lambda i: ops.window_attention(qd, None, odd, kps[i % n_bufs], vps[i % n_bufs], dtable, pos_b, slot_b, H, page,
+                                                       None, hd ** -0.5, None, None, fault, dstep, sink=sink))
+    t_like = _graph_time(lambda i: ops.window_attention(qd, None, odd, kps[i % n_bufs], vps[i % n_bufs], dtable, pos_b, slot_b, H, page,
+                                                        None, hd ** -0.5, None, None, fault, dstep))
+    put(f"attention with a keyless term, {B} decode rows at {ctx}", t_new, B * ctx * 2 * G * hd * 2, "GB/s", t_like)
+    del kps, vps
+    # ---- the norm in groups: two updates added, two outputs written, beside two launches of the plain fused norm
+    res = [torch.randn(n, d, device=dev) for _ in range(bufs)]
+    da, db = [torch.randn(n, d, **bf) for _ in range(bufs)], [torch.randn(n, d, **bf) for _ in range(bufs)]
+    o1, o2, scale = torch.empty(n, d, **bf), torch.empty(n, d, **bf), torch.ones(d, device=dev)
+    t_new = _graph_time(lambda i: ops.group_norm(res[i % bufs], da[i % bufs], db[i % bufs], 2, 1e-6, scale, o1, scale, o2), 12)
+
+    def twice(i):
+        ops.add_rmsnorm(res[i % bufs], da[i % bufs], scale, 1e-6, o1, kind="mean_eps")
+        ops.add_rmsnorm(res[i % bufs], db[i % bufs], scale, 1e-6, o2, kind="mean_eps")
+    t_like = _graph_time(twice, 12)
+    put(f"two updates, norm in groups, two outputs, {n} rows", t_new, n * d * (8 + 4 + 4), "GB/s", t_like, n * d * (16 + 4 + 4))
+    t_new = _graph_time(lambda i: ops.group_norm(res[i % bufs][:B], da[i % bufs][:B], db[i % bufs][:B], 2, 1e-6, scale, o1[:B], scale,
+                                                 o2[:B]), 12)
+    t_like = _graph_time(lambda i: (ops.add_rmsnorm(res[i % bufs][:B], da[i % bufs][:B], scale, 1e-6, o1[:B], kind="mean_eps"),
+                                    ops.add_rmsnorm(res[i % bufs][:B], db[i % bufs][:B], scale, 1e-6, o2[:B], kind="mean_eps")), 12)
+    put(f"two updates, norm in groups, two outputs, {B} rows", t_new, B * d * 16, "GB/s", t_like, B * d * 24)
+    # ---- the embedding with the hashed pair table beside the plain gather
+    vocab = 32768
+    tab, prs = torch.randn(vocab, d, **bf), torch.randn(4100, d, **bf)
+    toks = torch.randint(0, vocab, (n,), **i32)
+    prev = torch.zeros(8, 1, **i32)
+    t_new = _graph_time(lambda i: ops.embed_pairs(tab, prs, toks, pos, slot, last, prev, res[i % bufs], 2.0, 4099, 127, 17), 12)
+    t_like = _graph_time(lambda i: ops.embed_rows(tab, toks, res[i % bufs], 2.0), 12)
+    put(f"embedding with a pair table, {n} rows", t_new, n * d * (2 + 2 + 4), "GB/s", t_like, n * d * (2 + 4))
+    # ---- routed experts without gates (one matrix and an activation) beside the gated ones with as many weights
+    fe = max(64, F // (top + 1) // 64 * 64)
+    x = torch.randn(n, d, **bf)
+    wr = torch.randn(E, d, device=dev)
+    up1, up2 = torch.randn(E, fe * 3 // 2 // 64 * 64, d, **bf) * 0.02, torch.randn(E, 2, fe, d, **bf) * 0.02
+    f1 = up1.shape[1]
+    dn1, dn2 = torch.randn(E, d, f1, **bf) * 0.02, torch.randn(E, d, fe, **bf) * 0.02
+    ch, wt, _ = ops.moe_route(x, wr, None, None, 0, 0, top, scores="softmax_chosen")
+    t_new = _graph_time(lambda i: ops.moe_experts(x, ch, wt, up1, dn1, None, None, act="relu2"), 6)
+    t_like = _graph_time(lambda i: ops.moe_experts(x, ch, wt, up2, dn2, None, None), 6)
+    put(f"experts without gates, {n} rows", t_new, 2.0 * n * top * 2 * f1 * d, "TFLOP/s", t_like, 2.0 * n * top * 3 * fe * d)
+    t_new = _graph_time(lambda i: ops.moe_experts(x[:B], ch[:B], wt[:B], up1, dn1, None, None, act="relu2"), 12)
+    t_like = _graph_time(lambda i: ops.moe_experts(x[:B], ch[:B], wt[:B], up2, dn2, None, None), 12)
+    put(f"experts without gates, {B} decode rows", t_new, B * top * 2 * f1 * d * 2, "GB/s", t_like, B * top * 3 * fe * d * 2)
+    t_new = _graph_time(lambda i: ops.moe_route(x, wr, None, None, 0, 0, top, scores="softmax_chosen"), 12)
+    t_like = _graph_time(lambda i: ops.moe_route(x, wr, None, None, 0, 0, top), 12)
+    put(f"router, softmax over the chosen, {n} rows", t_new, n * d * 2, "GB/s", t_like)
+    return out
+
+
 def sampling(args):
     """The sampling kernel at ``--rows`` rows of ``--vocab`` logits, for the kinds of setting a row can have."""
     dev = "cuda"
@@ -786,7 +952,7 @@ def timeline(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "sampling", "timeline",
-                                     "seqmix", "latent-linear-routed", "differential-latent-forget", "all"])
+                                     "seqmix", "latent-linear-routed", "differential-latent-forget", "gated-space-tied", "all"])
     ap.add_argument("--rank", type=int, default=128, help="latent-linear-routed: compressed elements a token")
     ap.add_argument("--rot", type=int, default=64, help="latent-linear-routed: rotated elements a token")
     ap.add_argument("--experts", type=int, default=16)
@@ -837,6 +1003,8 @@ def main(argv=None):
         latent_linear_routed(args)
     if args.what in ("differential-latent-forget", "all"):
         differential_latent_forget(args)
+    if args.what in ("gated-space-tied", "all"):
+        gated_space_tied(args)
     return 0
 
 
