@@ -13,15 +13,19 @@
 
 namespace {
 
-// out = row * rsqrt(mean over the part + eps) * w, part by part; `row` (d floats) lies in shared memory and is complete.
-// Few parts: the whole CTA sums one part after the other; many: a warp a part.
+constexpr int FEW_GROUPS = 8;
+
+// out = row * rsqrt(mean over the part + eps) * w, part by part; `row` (d floats) lies in shared memory and is complete
+// (the caller has synchronised).  Up to FEW_GROUPS parts: every thread sums its share of every part in registers, one
+// reduction over the CTA gives all the parts' sums at once (in a fixed order: the same bits every time), and the outputs
+// leave in 16-byte vectors where the sizes allow; more parts: a warp a part.  `red`: FEW_GROUPS * 33 floats.
 template <typename O>
 __device__ __forceinline__ void grouped_norm_write(const float* row, int d, int groups, float eps, const float* __restrict__ w1,
                                                    O* __restrict__ out1, const float* __restrict__ w2, O* __restrict__ out2,
                                                    float* __restrict__ back, float* red) {
     const int per = d / groups;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-    if (groups * 2 >= nw) {
+    if (groups > FEW_GROUPS) {
         for (int g = warp; g < groups; g += nw) {
             const float* part = row + (size_t)g * per;
             float ss = 0.f;
@@ -38,19 +42,54 @@ __device__ __forceinline__ void grouped_norm_write(const float* row, int d, int 
         }
         return;
     }
-    for (int g = 0; g < groups; ++g) {
-        const float* part = row + (size_t)g * per;
-        float ss = 0.f;
-        for (int i = tid; i < per; i += blockDim.x) ss = fmaf(part[i], part[i], ss);
-        ss = block_sum(ss, red);
-        const float f = rsqrtf(ss / (float)per + eps);
-        for (int i = tid; i < per; i += blockDim.x) {
-            const int c = g * per + i;
-            const float v = part[i] * f;
-            if (back != nullptr) back[c] = v * w1[c];
-            else if (out1 != nullptr) out1[c] = from_f32<O>(v * w1[c]);
-            if (out2 != nullptr) out2[c] = from_f32<O>(v * w2[c]);
+    float part[FEW_GROUPS];
+#pragma unroll
+    for (int k = 0; k < FEW_GROUPS; ++k) part[k] = 0.f;
+    for (int i = tid; i < d; i += blockDim.x) {
+        const float v = row[i];
+        const int g = i / per;
+#pragma unroll
+        for (int k = 0; k < FEW_GROUPS; ++k) part[k] = (k == g) ? fmaf(v, v, part[k]) : part[k];
+    }
+#pragma unroll
+    for (int k = 0; k < FEW_GROUPS; ++k) {
+        if (k < groups) {
+            const float v = warp_sum(part[k]);
+            if (lane == 0) red[k * 33 + warp] = v;
         }
+    }
+    __syncthreads();
+    if (tid < groups) {
+        float t = 0.f;
+        for (int w = 0; w < nw; ++w) t += red[tid * 33 + w];
+        red[tid * 33 + 32] = rsqrtf(t / (float)per + eps);
+    }
+    __syncthreads();
+    constexpr int N = Vec16<O>::N;
+    const bool vec = per % N == 0 && back == nullptr &&
+                     (((uintptr_t)out1 | (uintptr_t)out2 | (uintptr_t)w1 | (uintptr_t)w2) % 16) == 0;
+    if (vec) {
+        for (int i = tid * N; i < d; i += blockDim.x * N) {
+            const float f = red[(i / per) * 33 + 32];
+            float a[N];
+            if (out1 != nullptr) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) a[j] = row[i + j] * f * w1[i + j];
+                Vec16<O>::store(out1 + i, a);
+            }
+            if (out2 != nullptr) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) a[j] = row[i + j] * f * w2[i + j];
+                Vec16<O>::store(out2 + i, a);
+            }
+        }
+        return;
+    }
+    for (int i = tid; i < d; i += blockDim.x) {
+        const float v = row[i] * red[(i / per) * 33 + 32];
+        if (back != nullptr) back[i] = v * w1[i];
+        else if (out1 != nullptr) out1[i] = from_f32<O>(v * w1[i]);
+        if (out2 != nullptr) out2[i] = from_f32<O>(v * w2[i]);
     }
 }
 
@@ -110,17 +149,46 @@ __global__ void __launch_bounds__(256)
 group_norm_kernel(float* __restrict__ res, const T* __restrict__ delta_a, const T* __restrict__ delta_b, int groups, float eps,
                   const float* __restrict__ w1, T* __restrict__ out1, const float* __restrict__ w2, T* __restrict__ out2,
                   int in_place, int d) {
-    extern __shared__ float row[];
-    __shared__ float red[33];
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[FEW_GROUPS * 33];
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = res[base + i];
-        if (delta_a != nullptr) v += to_f32(delta_a[base + i]);
-        if (delta_b != nullptr) v += to_f32(delta_b[base + i]);
-        if ((delta_a != nullptr || delta_b != nullptr) && !in_place) res[base + i] = v;
-        row[i] = v;
+    constexpr int N = Vec16<T>::N;
+    const bool any = delta_a != nullptr || delta_b != nullptr;
+    if (d % N == 0 && (((uintptr_t)res | (uintptr_t)delta_a | (uintptr_t)delta_b) % 16) == 0) {
+        for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+            float v[N], dv[N];
+#pragma unroll
+            for (int j = 0; j < N; j += 4) {
+                const float4 x = *reinterpret_cast<const float4*>(res + base + i + j);
+                v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
+            }
+            if (delta_a != nullptr) {
+                Vec16<T>::load(delta_a + base + i, dv);
+#pragma unroll
+                for (int j = 0; j < N; ++j) v[j] += dv[j];
+            }
+            if (delta_b != nullptr) {
+                Vec16<T>::load(delta_b + base + i, dv);
+#pragma unroll
+                for (int j = 0; j < N; ++j) v[j] += dv[j];
+            }
+#pragma unroll
+            for (int j = 0; j < N; j += 4) {
+                if (any && !in_place)
+                    *reinterpret_cast<float4*>(res + base + i + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                *reinterpret_cast<float4*>(row + i + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = res[base + i];
+            if (delta_a != nullptr) v += to_f32(delta_a[base + i]);
+            if (delta_b != nullptr) v += to_f32(delta_b[base + i]);
+            if (any && !in_place) res[base + i] = v;
+            row[i] = v;
+        }
     }
     __syncthreads();
     if (w1 == nullptr) return;
@@ -190,8 +258,8 @@ __global__ void __launch_bounds__(256)
 skip_gate_group_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ x, int ldx, const float* __restrict__ skip,
                             const T* __restrict__ z, int ldz, const float* __restrict__ w, int groups, float eps,
                             T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int H, int v_dim) {
-    extern __shared__ float row[];
-    __shared__ float red[33];
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[FEW_GROUPS * 33];
     pdl_launch_dependents();
     const int r = blockIdx.x;
     if (row_slot[r] < 0) return;
