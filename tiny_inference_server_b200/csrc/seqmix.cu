@@ -984,7 +984,8 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
 // columns a CTA takes: LANES lanes share a column of one head's state (lane p keeps the key channels p * DL .. + DL - 1
 // of it in registers) and add their partial sums with shuffles; a CTA takes COLS columns: 32 with four lanes each, or,
 // with eight lanes each, 64 (sixteen warps: a scheduler has four recurrences to switch between) or 16 (four times the
-// CTAs, for steps of few requests, where a head's columns are all the parallelism there is).  The
+// CTAs, for steps of few requests, where a head's columns are all the parallelism there is), or, with sixteen lanes
+// each, 8 (a prompt of one request: a thread's share of a token's work is halved again and twice the warps walk).  The
 // chunk's q^, k^ and g lie in shared memory with four floats of padding after every lane's share, so that the lanes of
 // a column read different banks with 16-byte loads.  A chunk is prepared by all threads, NT / 16 to a token; the raw
 // values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
@@ -1097,7 +1098,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
         if (c0 + DELTA_CHUNK < rows) fetch(c0 + DELTA_CHUNK);
         // With registers to spare (the narrow CTAs) a token's vectors are read from shared memory while the token
         // before is walked, so that the recurrence never waits for them.
-        constexpr bool AHEAD = NT <= 128 && LANES == 8;
+        constexpr bool AHEAD = NT <= 128 && LANES >= 8;
         float2 kn[AHEAD ? DL / 2 : 1], qn[AHEAD ? DL / 2 : 1], gn[AHEAD ? DL / 2 : 1];
         float vn = 0.f, bn = 0.f;
         auto ahead = [&](int t) {
@@ -1334,6 +1335,11 @@ static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const voi
             (const T*)b_in, ldb, (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps,      \
             q_scale, state, state_stride, (T*)out, ldo, o_raw, row_slot, row_last, seg_row0, segments, n, H, G, v_dim,       \
             decay_mode, gate_act, stream)));
+        if (v_dim % 8 == 0 && narrow >= 2) {            // sixteen lanes a column, 8 columns a CTA: one or two requests
+            TIS_DELTA_SPLIT(32, 2, 16, 8)
+            TIS_DELTA_SPLIT(64, 4, 16, 8)
+            TIS_DELTA_SPLIT(128, 8, 16, 8)
+        }
         if (v_dim % 64 == 0 && !narrow) {               // eight lanes a column, 64 columns a CTA
             TIS_DELTA_SPLIT(32, 4, 8, 64)
             TIS_DELTA_SPLIT(64, 8, 8, 64)

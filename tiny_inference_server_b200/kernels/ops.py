@@ -992,8 +992,17 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
 #: what a mixer's gate does to the projection it is made from
 GATE_ACTS = {"sigmoid": 0, "silu": 1}
 
-#: CTAs of 64 columns from which the delta rule keeps them (fewer: 16 columns a CTA, four times as many CTAs)
+#: CTAs of 64 columns from which the delta rule keeps them (fewer: 16 columns a CTA, four times as many CTAs; fewer even of
+#: those: 8 columns a CTA with sixteen lanes a column)
 DELTA_WIDE_MIN_CTAS = 2 * 148
+
+
+def _recurrence_spread(requests: Optional[int], num_heads: int, v_dim: int) -> int:
+    """How a head's state columns are shared out over CTAs: 0 64 columns a CTA, 1 16 columns, 2 8 columns with sixteen
+    lanes each; the fewer requests a step holds, the finer."""
+    if requests is None or requests * num_heads * max(1, v_dim // 64) >= DELTA_WIDE_MIN_CTAS:
+        return 0
+    return 1 if requests * num_heads * max(1, v_dim // 16) >= DELTA_WIDE_MIN_CTAS else 2
 
 
 def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, gate: Optional[torch.Tensor],
@@ -1013,7 +1022,7 @@ def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, ga
     launches CTAs for the requests only, not for every row."""
     lib = library()
     n = qkv.shape[0]
-    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    narrow = _recurrence_spread(requests, num_heads, v_dim)
     # widths that the kernel with a head's columns split over CTAs takes: the outputs pass through 32-bit scratch
     # and a second launch normalises them
     raw = None
@@ -1042,7 +1051,7 @@ def linear_attention(qkv: torch.Tensor, gate: Optional[torch.Tensor], decay: tor
     ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
     lib = library()
     n = qkv.shape[0]
-    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    narrow = _recurrence_spread(requests, num_heads, v_dim)
     raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qkv.device)
     global launches
     launches += 1
@@ -1066,7 +1075,7 @@ def forget_gate_recurrence(qv: torch.Tensor, f_in: torch.Tensor, lower: torch.Te
     and norm are 32-bit.  ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
     lib = library()
     n = qv.shape[0]
-    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    narrow = _recurrence_spread(requests, num_heads, v_dim)
     raw = None
     if lib.tis_delta_rule_splits(k_dim, v_dim):
         raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qv.device)
@@ -1174,7 +1183,7 @@ def gated_linear_attention(qkv: torch.Tensor, a_in: torch.Tensor, power: torch.T
     heads).  Gate, state and norm are 32-bit.  ``requests`` and ``segments`` as for ``delta_rule``."""
     lib = library()
     n = qkv.shape[0]
-    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    narrow = _recurrence_spread(requests, num_heads, v_dim)
     raw = None
     if lib.tis_delta_rule_splits(k_dim, v_dim):
         raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qkv.device)
@@ -1199,7 +1208,7 @@ def state_space_scan(cbx: torch.Tensor, dt_in: torch.Tensor, a_log: torch.Tensor
     float32.  ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
     lib = library()
     n = cbx.shape[0]
-    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    narrow = _recurrence_spread(requests, num_heads, v_dim)
     raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=cbx.device)
     _check(lib.tis_state_space_scan(_dt(cbx), _p(cbx), cbx.stride(0), _p(dt_in), dt_in.stride(0), _p(a_log), _p(dt_bias),
                                     _p(state), ctypes.c_size_t(state.stride(0)), _p(raw), _p(row_slot), _p(row_last), n,
