@@ -448,7 +448,7 @@ def kubolorn_config(width, heads, kv_heads, ffn, vocab, layers, experts=16, top=
     run twice in a row, so that ``layers`` layer runs come from ``layers - 2`` layers' weights."""
     fd = ffn * 3 // 2 // 64 * 64
     fe = max(64, ffn * 3 // 2 // top // 64 * 64)
-    gla = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    gla = {"heads": heads, "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64}
     par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                     "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
            "right": {"heads": heads, "vdim": 128, "state": 128, "groups": kv_heads, "norm_groups": kv_heads, "conv": 4},
@@ -458,7 +458,7 @@ def kubolorn_config(width, heads, kv_heads, ffn, vocab, layers, experts=16, top=
     n = max(3, layers - 2)
     kinds = [("gla", gla, dense), ("gla", gla, moe), ("gla", gla, dense), ("parallel", par, moe)]
     return dict(architecture="Kubolorn", vocab=vocab, width=width, norm={"eps": 1e-6, "groups": 2}, max_context=8192,
-                embedding={"scale": width ** 0.5, "bigram": {"buckets": 4099, "mul_prev": 127, "mul_cur": 17}},
+                embedding={"scale": width ** 0.5, "bigram": {"buckets": 4099, "mul_prev": 1009, "mul_cur": 31}},
                 canon={"taps": 4}, loop={"start": 1, "stop": 3, "times": 2},
                 layers=[{"type": kinds[i % 4][0], "mixer": json.loads(json.dumps(kinds[i % 4][1])),
                          "mlp": json.loads(json.dumps(kinds[i % 4][2]))} for i in range(n)])

@@ -71,11 +71,11 @@ K2 = _cfg(53, 40, [
 # widths that the tensor-core attention and the split recurrence kernels take; the attention layer inside the loop (a cache
 # plane per pass); every expert chosen
 K3 = _cfg(200, 128, [
-    {"type": "gla", "mixer": _gla(4, 64, 64, tau=16.0), "mlp": _moe(64, 4, 4)},
+    {"type": "gla", "mixer": _gla(4, 64, 64, tau=12.0), "mlp": _moe(64, 4, 4)},
     {"type": "parallel", "mixer": _par(8, 1, 64, 32, 4, 64, 64, 2, 2, 4, base=500.0, scaling=(2.0, 32, 4.0, 0.5)),
      "mlp": _dense(256)},
     {"type": "gla", "mixer": _gla(2, 32, 64, tau=4.0), "mlp": _dense(64)},
-], groups=2, taps=4, buckets=509, muls=(127, 17), scale=11.3, loop=(0, 2, 3))
+], groups=2, taps=4, buckets=401, muls=(113, 19), scale=11.3, loop=(0, 2, 3))
 # a convolution of one tap (no history at all) in front of the sublayers; a loop that runs once; groups of one element's
 # worth of heads; two parallel layers with different sizes (two cache groups)
 K4 = _cfg(64, 48, [
@@ -796,7 +796,7 @@ def random_configuration(seed):
     rng.shuffle(kinds)
     for kind in kinds + [pick(kinds) for _ in range(rng.randint(0, 3))]:
         if kind == "gla":
-            mixer = _gla(pick([1, 2, 3, 4]), pick([8, 16, 32, 48, 64]), pick([8, 16, 32, 64, 96]), tau=pick([1.0, 4.0, 16.0, 64.0]))
+            mixer = _gla(pick([1, 2, 3, 4]), pick([8, 16, 32, 48, 64]), pick([8, 16, 32, 64, 96]), tau=pick([1.0, 4.0, 12.0, 64.0]))
         else:
             kv = pick([1, 2, 3])
             dim = pick([8, 16, 24, 32, 64, 96])
@@ -817,8 +817,8 @@ def random_configuration(seed):
     loop = (start, rng.randint(start, n), rng.randint(1, 3)) if rng.random() < 0.8 else None
     # (a norm over a group of fewer than sixteen elements makes a model of random weights ill-conditioned in bfloat16)
     groups = pick([g for g in (1, 2, 3, 4, 8) if width % g == 0 and width // g >= 16])
-    cfg = _cfg(rng.randint(40, 300), width, layers, groups=groups, taps=pick([1, 2, 3, 4, 5]), buckets=pick([1, 17, 509, 4099]),
-               muls=(pick([0, 1, 127, 100003]), pick([1, 17, 31])), scale=pick([0.5, 1.0, 8.0, 13.9]), loop=loop,
+    cfg = _cfg(rng.randint(40, 300), width, layers, groups=groups, taps=pick([1, 2, 3, 4, 5]), buckets=pick([1, 17, 523, 4099]),
+               muls=(pick([0, 1, 131, 100003]), pick([1, 19, 31])), scale=pick([0.5, 1.0, 8.0, 12.0]), loop=loop,
                eps=pick([1e-5, 1e-6]))
     return cfg, pick([8, 16, 16, 32])
 

@@ -617,7 +617,7 @@ def gated_space_tied(args):
     # ---- gated linear attention beside the recurrence whose forget gate writes (the same walk of a matrix state with a
     # gate per key channel; this one also reads keys) and, for decode rows, the same
     rows = [torch.randn(n, 4 * nv, **bf) for _ in range(2)]
-    power, a_bias, nw = torch.full((H,), 1 / 16, device=dev), torch.full((nv,), 3.0, device=dev), torch.ones(hd, device=dev)
+    power, a_bias, nw = torch.full((H,), 1 / 8, device=dev), torch.full((nv,), 3.0, device=dev), torch.ones(hd, device=dev)
     lower, fb = torch.rand(nv, device=dev) * 0.9, torch.zeros(nv, device=dev)
     gate = torch.randn(n, nv, **bf)
     st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
@@ -726,7 +726,7 @@ def gated_space_tied(args):
     tab, prs = torch.randn(vocab, d, **bf), torch.randn(4100, d, **bf)
     toks = torch.randint(0, vocab, (n,), **i32)
     prev = torch.zeros(8, 1, **i32)
-    t_new = _graph_time(lambda i: ops.embed_pairs(tab, prs, toks, pos, slot, last, prev, res[i % bufs], 2.0, 4099, 127, 17), 12)
+    t_new = _graph_time(lambda i: ops.embed_pairs(tab, prs, toks, pos, slot, last, prev, res[i % bufs], 2.0, 4099, 1009, 31), 12)
     t_like = _graph_time(lambda i: ops.embed_rows(tab, toks, res[i % bufs], 2.0), 12)
     put(f"embedding with a pair table, {n} rows", t_new, n * d * (2 + 2 + 4), "GB/s", t_like, n * d * (2 + 4))
     # ---- routed experts without gates (one matrix and an activation) beside the gated ones with as many weights

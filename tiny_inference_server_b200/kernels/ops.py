@@ -999,10 +999,12 @@ DELTA_WIDE_MIN_CTAS = 2 * 148
 
 def _recurrence_spread(requests: Optional[int], num_heads: int, v_dim: int) -> int:
     """How a head's state columns are shared out over CTAs: 0 64 columns a CTA, 1 16 columns, 2 8 columns with sixteen
-    lanes each; the fewer requests a step holds, the finer."""
+    lanes each; the fewer requests and heads a step holds, the finer."""
     if requests is None or requests * num_heads * max(1, v_dim // 64) >= DELTA_WIDE_MIN_CTAS:
         return 0
-    return 1 if requests * num_heads * max(1, v_dim // 16) >= DELTA_WIDE_MIN_CTAS else 2
+    # the finest geometry only where all of its CTAs are resident at once (two an SM by registers): a second wave of a
+    # walk as long as the prompt would double the time
+    return 2 if requests * num_heads * max(1, v_dim // 8) <= DELTA_WIDE_MIN_CTAS else 1
 
 
 def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, gate: Optional[torch.Tensor],
@@ -1277,7 +1279,7 @@ def rotate_tie_store(qk: torch.Tensor, num_heads: int, kv_heads: int, dim: int, 
     """Between the projections and the cache of an attention whose values are its keys before rotation.  A row of ``qk``:
     H query heads, then G key heads, ``dim`` elements each.  The first ``rot`` elements of every head are rotated by the
     row's position (element i with i + rot / 2; ``cos``, ``sin`` (positions, rot / 2) float32): queries in place, keys into
-    the key rows of the row's page; the keys as projected go into the value rows."""
+    the key rows of the row's page; the unrotated keys go into the value rows."""
     lib = library()
     n = qk.shape[0]
     kps, khs = _page_strides(k_pages, dim)

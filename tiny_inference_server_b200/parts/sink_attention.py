@@ -19,7 +19,7 @@ class TiedValueAttention(Mixer):
     * ``position`` (a ``RotaryHalf`` family member) rotates the first ``position.rotary_dim`` elements of every query and
       key head by the token's position; the values stay unrotated;
     * ``score = (q . k) * scale`` over the keys ``0..p`` (``window`` W: ``p - W + 1..p``), softmax in 32-bit; with
-      ``has_sink`` its denominator holds one more term ``exp(sink[h])`` that has no key and no value;
+      ``has_sink`` its denominator holds one more term ``exp(sink[h])``, a term without a key or a value behind it;
     * ``Wo`` on the heads' outputs side by side.
 
     The cache holds, per token and key head, the rotated key as the key row and the unrotated key as the value row.

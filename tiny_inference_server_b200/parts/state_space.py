@@ -22,7 +22,7 @@ class SelectiveStateSpace(Mixer):
     * ``dt = softplus(dt + dt_bias)`` (no clamp); per head ``S <- exp(-exp(A_log) dt) S + dt B x^T``,
       ``y = S^T C + D x`` (y is read from the updated S);
     * the heads' y side by side times ``silu(z)``, then an RMS norm in ``norm_groups`` equal parts (each by its own root
-      mean square, ``eps`` inside the root) times ``norm``: the gate comes before the norm; then ``W_o``.
+      mean square, ``eps`` inside the root) times ``norm`` (gated first, normed after); then ``W_o``.
 
     Tensor names below the prefix: ``in, o`` (stored (out, in)), ``conv, conv.b``, ``dt_bias, A_log, D``, ``norm``.  On
     the device the input projection's columns lie as ``C | B | x | z | dt`` (what the recurrence's kernel takes as
