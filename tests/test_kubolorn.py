@@ -837,11 +837,13 @@ def test_configurations_drawn_at_random(seed, dtype, tmp_path):
     ref = {rid: plain.plain_forward(c, W, toks).numpy() for rid, toks in seqs.items()}
     steps = trace_tools.trace_mixed(seqs, max_live=3, prefill_sizes=(64, 2, 130, 17))
     # A logit row that has nothing to do with the right one differs from it by about 1.4; a position whose router chose
-    # another expert in bfloat16 may differ by about 1.  Some of the drawn models (a width of 32, a span of routed layers
-    # run three times) are so ill-conditioned that in bfloat16 one position in ten leaves the tolerance; float32, which
-    # runs the same steps, holds all but one in a hundred (a router's choice at the edge flips there too, by less).
+    # another expert in bfloat16 may differ by about 1, and the recurrent states carry the difference on through the
+    # positions after it.  Some of the drawn models (a width of 32, a span of routed layers run three times) are so
+    # ill-conditioned that in bfloat16 runs of positions leave the tolerance, however the request is cut (fed whole it
+    # differs at the same positions by the same amounts); float32, which runs the same steps, holds all but one in a
+    # hundred (a router's choice at the edge flips there too, by less).
     _replay_and_compare(raw, page, folder, seqs, ref, steps, str(tmp_path / "out"), dtype, "cuda:0", TOL[dtype], max_live=3,
-                        poison=True, shuffle=True, outliers={"float32": 0.01, "bfloat16": 0.12}[dtype],
+                        poison=True, shuffle=True, outliers={"float32": 0.01, "bfloat16": 0.3}[dtype],
                         cap={"float32": 0.1, "bfloat16": 1.3}[dtype])
 
 
