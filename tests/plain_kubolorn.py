@@ -1,7 +1,7 @@
 """Plain, slow implementation of the Kubolorn decoder: whole sequences, no cache, one function per
 mechanism, ordinary tensor arithmetic in float64, token by token where the design is a recurrence.  It takes
-the configuration as the dictionary of ``config.json`` and the weights as a dictionary of tensors by name,
-and shares no code with the engine package.
+the configuration as the dictionary of ``config.json`` and the weights as a dictionary of tensors by name (it
+reads both on its own) and shares no code with the engine package.
 
 Notation: ``L`` tokens of one sequence, ``t`` a position from 0, ``u`` the input of a sublayer, ``W[name]`` a
 tensor stored ``(out, in)``.
@@ -22,6 +22,19 @@ import math
 import torch
 
 F64 = torch.float64
+
+
+def read_config(folder: str) -> dict:
+    import json
+    import os
+    with open(os.path.join(folder, "config.json")) as f:
+        return json.load(f)
+
+
+def read_weights(folder: str, dtype=F64) -> dict:
+    import os
+    from safetensors.torch import load_file
+    return {k: v.to(dtype) for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
 
 
 def silu(z):
