@@ -1071,6 +1071,8 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
             }
             const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.f / sqrtf(sk + unit_eps);
+            // a decay per head is one number for all of a token's key channels: made once, not once a channel
+            const float g_head = (a_step == 0 && !plain && !forget && !gated) ? expf(-decay_rate * softplus_f(ra[0] + bias[0])) : 0.f;
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
                 const int ch = sub * CH + i;
@@ -1083,11 +1085,11 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
                 } else if (gated || stepped) {
                     qs[pt][at] = rq[i] * q_scale;
                     ks[pt][at] = rk[i];
-                    gs[pt][at] = expf(-decay_rate * softplus_f(gated ? -(ra[i] + bias[i]) : ra[i] + bias[i]));
+                    gs[pt][at] = gated ? expf(-decay_rate * softplus_f(-(ra[i] + bias[i]))) : g_head;
                 } else {
                     qs[pt][at] = plain ? silu_f(rq[i]) : rq[i] * fq;
                     ks[pt][at] = plain ? silu_f(rk[i]) : rk[i] * fk;
-                    gs[pt][at] = plain ? decay_rate : expf(-decay_rate * softplus_f(ra[i] + bias[i]));
+                    gs[pt][at] = plain ? decay_rate : (a_step == 0 ? g_head : expf(-decay_rate * softplus_f(ra[i] + bias[i])));
                 }
             }
 #pragma unroll
